@@ -41,6 +41,7 @@ Json spec_json(const ModelSpec& spec) {
     for (const LayerSpec& l : spec.layers) {
         Json lj = Json::object();
         lj.set("arrangement", l.arrangement);
+        lj.set("params", l.params);
         Json parts = Json::object();
         for (const auto& p : l.parts) parts.set(p.first, p.second.to_json());
         lj.set("parts", parts);

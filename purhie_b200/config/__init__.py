@@ -38,7 +38,7 @@ class ModelConfig:
 
     @property
     def architecture(self) -> str:
-        return self._values["architectures"][0]
+        return _architecture_of(self._values)
 
     def to_dict(self) -> Dict:
         d = dict(self._values)
@@ -55,6 +55,12 @@ class ModelConfig:
         """The description the generic decoder is assembled from: embedding, layers (arrangement and named
         sub-parts, each {kind, params}), the run order, final norm and head."""
         return native.answer(native.lib().qe_model_spec(self.to_json().encode()))
+
+
+def _architecture_of(d: Dict) -> str:
+    """The name a config.json dictionary gives: the first of ``architectures``, or ``architecture``."""
+    names = d.get("architectures")
+    return names[0] if names else d["architecture"]
 
 
 class Qwen3Config(ModelConfig):
@@ -75,7 +81,7 @@ class Qwen3Config(ModelConfig):
 def load_config(model_dir: str) -> ModelConfig:
     """Read ``model_dir/config.json`` (raises :class:`ConfigError`: missing, not JSON, unknown architecture)."""
     d = native.answer(native.lib().qe_config_load(str(model_dir).encode()))
-    return ModelConfig.from_dict(d) if d["architectures"][0] != "Qwen3ForCausalLM" else Qwen3Config.from_dict(d)
+    return ModelConfig.from_dict(d) if _architecture_of(d) != "Qwen3ForCausalLM" else Qwen3Config.from_dict(d)
 
 
 def registered_architectures() -> List[str]:

@@ -62,10 +62,12 @@ Json read_config_json(const std::string& model_dir) {
 }
 
 std::string architecture_name(const Json& d) {
+    // a list of names under 'architectures' (the first counts), or one name under 'architecture'
     const Json* a = d.find("architectures");
-    if (!a || !a->is_array() || a->size() == 0 || !(*a)[0].is_string())
-        throw ConfigError("config.json: 'architectures' must be a non-empty list of names");
-    return (*a)[0].as_string();
+    if (a && a->is_array() && a->size() != 0 && (*a)[0].is_string()) return (*a)[0].as_string();
+    const Json* one = d.find("architecture");
+    if (!a && one && one->is_string()) return one->as_string();
+    throw ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)");
 }
 
 std::unique_ptr<ModelConfig> config_from_json(const Json& d) {
@@ -330,9 +332,14 @@ ModelSpec Qwen3Config::build_spec() const {
     return spec;
 }
 
+void register_bozosun_architecture();
+
 void register_builtin_architectures() {
     static std::once_flag once;
-    std::call_once(once, [] { register_architecture("Qwen3ForCausalLM", Qwen3Config::read); });
+    std::call_once(once, [] {
+        register_architecture("Qwen3ForCausalLM", Qwen3Config::read);
+        register_bozosun_architecture();
+    });
 }
 
 }  // namespace qe

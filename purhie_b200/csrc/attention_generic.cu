@@ -2,6 +2,7 @@
 // arithmetic.  It is the whole attention of the 32-bit path, the reference the fast kernels are tested
 // against, and the refuge for head sizes the fast kernels do not take.
 //
+// Values may have another width (DV) than keys (D); the output row of a head is DV wide.
 // One warp per (token row, query head).  The row at absolute position z of a request sees the cached
 // positions lo .. z, lo = max(0, z - window + 1) (window 0: lo = 0).  Keys are taken 32 at a time
 // starting from lo: each lane scores one key (the whole dot product in one lane, in d order), the warp
@@ -26,7 +27,7 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
                                          const TKV* __restrict__ v_base, long long page_stride, int page_size,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
-                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale) {
+                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV) {
     __shared__ float qs[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -51,9 +52,9 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
         const TKV* vrow = nullptr;
         if (p <= z) {
             const int page = table[p / page_size];
-            const size_t off = (size_t)page * page_stride + ((size_t)g * page_size + p % page_size) * D;
-            const TKV* krow = k_base + off;
-            vrow = v_base + off;
+            const size_t at = (size_t)g * page_size + p % page_size;
+            const TKV* krow = k_base + (size_t)page * page_stride + at * D;
+            vrow = v_base + (size_t)page * page_stride + at * DV;
             float dot = 0.0f;
             for (int d = 0; d < D; ++d) dot += qs[warp][d] * to_float<TKV>(krow[d]);
             s = dot * scale;
@@ -72,17 +73,17 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
 #pragma unroll
             for (int i = 0; i < MAX_D / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) acc[i] += pj * to_float<TKV>(vj[d]);
+                if (d < DV) acc[i] += pj * to_float<TKV>(vj[d]);
             }
         }
         m = m_new;
     }
-    TO* o = out + ((size_t)t * HQ + h) * D;
+    TO* o = out + ((size_t)t * HQ + h) * DV;
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) o[d] = from_float<TO>(acc[i] * inv);
+        if (d < DV) o[d] = from_float<TO>(acc[i] * inv);
     }
 }
 
@@ -91,21 +92,22 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
 PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_base, const void* v_base, int kv_dtype,
                                    long long page_stride, int page_size, const int32_t* block_table,
                                    int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
-                                   int out_dtype, int T, int HQ, int HKV, int D, int window, float scale,
+                                   int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
                                    cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || T < 0 || HQ < 1 || HKV < 1 ||
         D < 1 || page_size < 1 || window < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) ||
         !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "attention_generic: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
     if (HQ % HKV) return fail(PH_ERR_ARG, "attention_generic: %d query heads are not a multiple of %d kv heads", HQ, HKV);
-    if (D > MAX_D) return fail(PH_ERR_UNSUPPORTED, "attention_generic: head_dim %d exceeds the supported %d", D, MAX_D);
+    if (DV <= 0) DV = D;                     // values as wide as keys
+    if (D > MAX_D || DV > MAX_D) return fail(PH_ERR_UNSUPPORTED, "attention_generic: head_dim %d / %d exceeds the supported %d", D, DV, MAX_D);
     if (T == 0) return PH_OK;
     const long long items = (long long)T * HQ;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
 #define LAUNCH(TQ, TKV, TO)                                                                                    \
     attention_generic_kernel<TQ, TKV, TO><<<blocks, WARPS * 32, 0, stream>>>(                                  \
         (const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, table_stride, \
-        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale)
+        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV)
     PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TO))));
 #undef LAUNCH
     return check_launch("attention_generic");

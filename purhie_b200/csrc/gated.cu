@@ -1,0 +1,48 @@
+// Gated activations over rows laid out [g0, u0, g1, u1, ...] (gate and up rows of the weight interleaved, as the
+// SwiGLU kernel reads them), with the gate's family as a parameter:
+//   kind 0 (silu):           out = g / (1 + exp(-g)) * u
+//   kind 1 (clamped swish):  g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(alpha * g') * (u' + shift)
+// The sums over split-K partial results and the activation are float32.
+#include "common.cuh"
+
+namespace {
+
+using namespace ph;
+
+__device__ __forceinline__ float gated(float g, float u, int kind, float alpha, float limit, float shift) {
+    if (kind == 0) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + shift);
+}
+
+template <typename TI, typename TO>
+__global__ void glu_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out, int FF,
+                           long long total, int kind, float alpha, float limit, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const TI* g = gu + idx * 2;
+    float gv = 0.0f, uv = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        gv += to_float<TI>(g[(size_t)s * split_stride]);
+        uv += to_float<TI>(g[(size_t)s * split_stride + 1]);
+    }
+    out[idx] = from_float<TO>(gated(gv, uv, kind, alpha, limit, shift));
+}
+
+}  // namespace
+
+PH_EXPORT int ph_glu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out, int out_dtype, int T,
+                     int FF, int kind, float alpha, float limit, float shift, cudaStream_t stream) {
+    if (!gate_up || !out || T < 0 || FF < 1 || splits < 1 || kind < 0 || kind > 1 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "glu: bad arguments (T %d, FF %d, kind %d)", T, FF, kind);
+    const long long total = (long long)T * FF;
+    if (total == 0) return PH_OK;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+        launch_overlapped(glu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)gate_up, splits, split_stride,
+                          (TO*)out, FF, total, kind, alpha, limit, shift)));
+    return check_launch("glu");
+}

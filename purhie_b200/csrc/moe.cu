@@ -1,0 +1,219 @@
+// Routing of a mixture of experts and the products of the chosen experts, all on the device (no count ever goes
+// to the host, so a step with routing can be captured as a graph).
+//
+//   route_topk     per token: the `top` largest of its float32 router logits (+ bias; the lower index wins a tie),
+//                  and the softmax over the chosen logits alone.
+//   route_sort     the (token, choice) pairs sorted by expert: position of each pair, pair at each position, and a
+//                  list of row tiles (expert, first position, rows) that never cross from one expert to the next.
+//   gemm_grouped   y[i] = W[expert of i] x[source row of i] for the sorted positions i, tile by tile; float32
+//                  multiply-add on the CUDA cores with k ascending inside one thread (the order of gemm_simple),
+//                  so a row's result depends on neither its place in the batch nor its place among the expert's rows.
+//   route_combine  out[t] = sum over the token's choices, in the order of the choices, weight * y[position of (t, j)].
+#include "common.cuh"
+
+namespace {
+
+using namespace ph;
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+constexpr int MAX_TOP = 32;
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int top,
+                                  int32_t* __restrict__ choice, float* __restrict__ weight, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * E;
+    int picked[MAX_TOP];
+    float value[MAX_TOP];
+    for (int j = 0; j < top; ++j) {
+        int best = -1;
+        float best_v = 0.0f;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int i = 0; i < j; ++i) taken |= picked[i] == e;
+            if (taken) continue;
+            const float v = z[e] + (bias ? bias[e] : 0.0f);
+            if (best < 0 || v > best_v) { best = e; best_v = v; }
+        }
+        picked[j] = best;
+        value[j] = best_v;
+    }
+    const float largest = value[0];                       // the first pick
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) { value[j] = expf(value[j] - largest); sum += value[j]; }
+    for (int j = 0; j < top; ++j) {
+        choice[(size_t)t * top + j] = picked[j];
+        weight[(size_t)t * top + j] = value[j] / sum;
+    }
+}
+
+// One block.  counts -> offsets -> a position for every pair; tiles[3 * i] = (expert, first position, rows), rows 0
+// for the tiles that are left over.
+__global__ void route_sort_kernel(const int32_t* __restrict__ choice, int R, int E, int32_t* __restrict__ position,
+                                  int32_t* __restrict__ pair_at, int32_t* __restrict__ tiles, int max_tiles,
+                                  int32_t* __restrict__ cursor /* [3 * E + 1] scratch */) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int32_t* count = cursor;            // [E]
+    int32_t* offset = cursor + E;       // [E + 1]
+    int32_t* fill = cursor + 2 * E + 1; // [E]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = fill[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < R; i += blockDim.x) atomicAdd(&count[choice[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < E; ++e) {
+            offset[e] = at;
+            for (int r0 = 0; r0 < count[e] && tile < max_tiles; r0 += BM, ++tile) {
+                tiles[3 * tile] = e;
+                tiles[3 * tile + 1] = at + r0;
+                tiles[3 * tile + 2] = min(BM, count[e] - r0);
+            }
+            at += count[e];
+        }
+        offset[E] = at;
+        for (; tile < max_tiles; ++tile) { tiles[3 * tile] = 0; tiles[3 * tile + 1] = 0; tiles[3 * tile + 2] = 0; }
+    }
+    __syncthreads();
+    // which of an expert's places a pair gets is left to chance: a row's result does not depend on its place
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        const int e = choice[i];
+        const int at = offset[e] + atomicAdd(&fill[e], 1);
+        position[i] = at;
+        pair_at[at] = i;
+    }
+}
+
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(256) gemm_grouped_kernel(const TX* __restrict__ x, const int32_t* __restrict__ pair_at,
+                                                           int pairs_per_row, const TW* __restrict__ w,
+                                                           const int32_t* __restrict__ tiles, TY* __restrict__ y, int N, int K) {
+    __shared__ float xs[BK][BM + 1];
+    __shared__ float ws[BK][BN + 1];
+    __shared__ int src_row[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    if (rows == 0) return;
+    const int tid = threadIdx.x;
+    const int n0 = blockIdx.x * BN;
+    const TW* we = w + (size_t)expert * N * K;
+    // the source row of x for each row of the tile: the pair's token (pairs_per_row pairs per token), or the position itself
+    if (tid < BM) src_row[tid] = tid < rows ? (pair_at ? pair_at[row0 + tid] / pairs_per_row : row0 + tid) : -1;
+    __syncthreads();
+    const int tr = tid / (BN / TN), tc = tid % (BN / TN);
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = tid + e * 256;
+            const int r = idx / BK, kk = idx % BK;
+            const int k = k0 + kk;
+            float xv = 0.0f, wv = 0.0f;
+            if (k < K) {
+                if (src_row[r] >= 0) xv = to_float<TX>(x[(size_t)src_row[r] * K + k]);
+                if (n0 + r < N) wv = to_float<TW>(we[(size_t)(n0 + r) * K + k]);
+            }
+            xs[kk][r] = xv;
+            ws[kk][r] = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = xs[kk][tr * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = ws[kk][tc * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = tr * TM + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tc * TN + j;
+            if (n < N) y[(size_t)(row0 + m) * N + n] = from_float<TY>(acc[i][j]);
+        }
+    }
+}
+
+template <typename TY>
+__global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
+                                     int top, float* __restrict__ out, int E_out, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int)(idx / E_out), c = (int)(idx % E_out);
+    float acc = 0.0f;
+    for (int j = 0; j < top; ++j)
+        acc += weight[(size_t)t * top + j] * to_float<TY>(y[(size_t)position[(size_t)t * top + j] * E_out + c]);
+    out[idx] = acc;
+}
+
+}  // namespace
+
+PH_EXPORT int ph_route_topk(const float* logits, const float* bias, int T, int E, int top, int32_t* choice, float* weight,
+                            cudaStream_t stream) {
+    if (!logits || !choice || !weight || T < 0 || E < 1 || top < 1 || top > E)
+        return fail(PH_ERR_ARG, "route_topk: bad arguments (T %d, experts %d, top %d)", T, E, top);
+    if (top > MAX_TOP) return fail(PH_ERR_UNSUPPORTED, "route_topk: top %d exceeds the supported %d", top, MAX_TOP);
+    if (T == 0) return PH_OK;
+    launch_overlapped(route_topk_kernel, dim3((T + 63) / 64), dim3(64), 0, stream, logits, bias, E, top, choice, weight, T);
+    return check_launch("route_topk");
+}
+
+PH_EXPORT int ph_route_max_tiles(int R, int E) { return (R + BM - 1) / BM + E; }
+
+// choice [R] (R = tokens x top) -> position [R], pair_at [R], tiles [3 * max_tiles]; scratch: 3 * E + 1 int32.
+PH_EXPORT int ph_route_sort(const int32_t* choice, int R, int E, int32_t* position, int32_t* pair_at, int32_t* tiles,
+                            int max_tiles, int32_t* scratch, cudaStream_t stream) {
+    if (!choice || !position || !pair_at || !tiles || !scratch || R < 0 || E < 1 || max_tiles < ph_route_max_tiles(R, E))
+        return fail(PH_ERR_ARG, "route_sort: bad arguments (pairs %d, experts %d, tiles %d)", R, E, max_tiles);
+    if (R == 0) return PH_OK;
+    launch_overlapped(route_sort_kernel, dim3(1), dim3(E < 256 ? 256 : 1024), 0, stream, choice, R, E, position, pair_at, tiles,
+                      max_tiles, scratch);
+    return check_launch("route_sort");
+}
+
+// y [R, N] at the sorted positions; x rows are looked up through pair_at / pairs_per_row (null: x is already sorted);
+// w [experts, N, K].
+PH_EXPORT int ph_gemm_grouped(const void* x, int x_dtype, const int32_t* pair_at, int pairs_per_row, const void* w, int w_dtype,
+                              const int32_t* tiles, int max_tiles, void* y, int y_dtype, int N, int K, cudaStream_t stream) {
+    if (!x || !w || !tiles || !y || max_tiles < 1 || N < 1 || K < 1 || pairs_per_row < 1 || !valid_dtype(x_dtype) ||
+        !valid_dtype(w_dtype) || !valid_dtype(y_dtype))
+        return fail(PH_ERR_ARG, "gemm_grouped: bad arguments (tiles %d, N %d, K %d)", max_tiles, N, K);
+    if (max_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "gemm_grouped: %d row tiles exceed the supported 65535", max_tiles);
+    dim3 grid((N + BN - 1) / BN, max_tiles);
+#define LAUNCH(TX, TW, TY)                                                                                                \
+    launch_overlapped(gemm_grouped_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (const TX*)x, pair_at, pairs_per_row, \
+                      (const TW*)w, tiles, (TY*)y, N, K)
+    PH_DISPATCH(x_dtype, TX, PH_DISPATCH(w_dtype, TW, PH_DISPATCH(y_dtype, TY, LAUNCH(TX, TW, TY))));
+#undef LAUNCH
+    return check_launch("gemm_grouped");
+}
+
+PH_EXPORT int ph_route_combine(const void* y, int y_dtype, const int32_t* position, const float* weight, int T, int top, int E_out,
+                               float* out, cudaStream_t stream) {
+    if (!y || !position || !weight || !out || T < 0 || top < 1 || E_out < 1 || !valid_dtype(y_dtype))
+        return fail(PH_ERR_ARG, "route_combine: bad arguments (T %d, top %d, width %d)", T, top, E_out);
+    const long long total = (long long)T * E_out;
+    if (total == 0) return PH_OK;
+    PH_DISPATCH(y_dtype, TY, launch_overlapped(route_combine_kernel<TY>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                               (const TY*)y, position, weight, top, out, E_out, total));
+    return check_launch("route_combine");
+}

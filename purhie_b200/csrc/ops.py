@@ -100,12 +100,12 @@ _SIGNATURES = {
         "ph_qk_norm_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
                                      c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
-                                     c_float, c_void_p],
+                                     c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
         "ph_add_weight_sumsq": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int,
                                 c_void_p, c_int, c_void_p],
         "ph_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                 c_void_p],
+                                 c_int, c_void_p],
         "ph_gemm_simple": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ph_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
         "ph_argmax_parts": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p],
@@ -274,7 +274,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: tor
          _ptr(k_norm), float(eps), _ptr(cos_sin), n_rot, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(q_out),
          _code(q_out.dtype), _ptr(k_base), _ptr(v_base), kv_code, page_stride, page_size, T, num_heads, num_kv_heads,
          head_dim, 1 if interleaved else 0, _ptr(row_sumsq), 0 if row_sumsq is None else row_sumsq.shape[-1], row_width,
-         float(row_eps), _stream())
+         float(row_eps), 0, None, None, 0, _stream())
     return q_out
 
 
@@ -291,7 +291,7 @@ def attention_generic(q: torch.Tensor, k_base: torch.Tensor, v_base: torch.Tenso
         raise KernelError("attention_generic: K and V must share a dtype")
     call("core", "ph_attention_generic", _ptr(q), _code(q.dtype), _ptr(k_base), _ptr(v_base), _code(k_base.dtype),
          page_stride, page_size, _ptr(block_table), block_table.shape[-1], _ptr(row_seg), _ptr(positions), _ptr(out),
-         _code(out.dtype), T, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), _stream())
+         _code(out.dtype), T, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), 0, _stream())
     return out
 
 

@@ -4,7 +4,10 @@
 // One warp per (token, head).  For a q or k head: optional bias, v = v * rsqrt(mean_D(v^2) + eps) * w,
 // then rotate-half pairs (i, i + n_rot/2): (a, b) -> (a cos - b sin, a sin + b cos) with the angle of the
 // token's absolute position (interleaved = 1 pairs (2i, 2i + 1) instead); dimensions >= n_rot pass
-// through.  A v head is only biased and copied.  The table row of a position holds n_rot / 2 cosines, then
+// through.  A v head (DV wide, which need not be the width of a key) is biased and copied, or, with value mixing,
+// blended with the values that the first mixing layer of the step left for the same token:
+// v <- (1 - lambda) v + lambda v_first (mode 2), that first layer storing its own v as v_first (mode 1); the blended
+// v is what goes to the cache.  The table row of a position holds n_rot / 2 cosines, then
 // n_rot / 2 sines, one per pair.
 // Sums and angles are float32; the cos/sin table is made on the host in double precision.
 // Reference: src/attention.hip:273-313 (attn_prep: bias, norm, rotation, cache write), :219-240
@@ -42,22 +45,25 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
                                     int n_rot, int max_pos, const int32_t* __restrict__ positions,
                                     const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                     TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                    int page_size, int HQ, int HKV, int D, int interleaved, RowFactor rf) {
+                                    int page_size, int HQ, int HKV, int D, int interleaved, RowFactor rf, int DV,
+                                    float* __restrict__ v_first, const float* __restrict__ v_lambda, int v_mode) {
     __shared__ float buf[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * WARPS + warp;
     const int t = blockIdx.x;
     const int n_heads = HQ + 2 * HKV;
     if (head >= n_heads) return;
-    const int width = n_heads * D;
-    const TI* src = qkv + (size_t)t * width + (size_t)head * D;
-    const float* b = bias ? bias + (size_t)head * D : nullptr;
+    const int width = (HQ + HKV) * D + HKV * DV;
     const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
+    const size_t head_at = (is_q || is_k) ? (size_t)head * D : (size_t)(HQ + HKV) * D + (size_t)(head - HQ - HKV) * DV;
+    const int hd = (is_q || is_k) ? D : DV;                    // this head's width
+    const TI* src = qkv + (size_t)t * width + head_at;
+    const float* b = bias ? bias + head_at : nullptr;
     float* row = buf[warp];
     const float rs = row_factor(rf, t);
 
     float ss = 0.0f;
-    for (int d = lane; d < D; d += 32) {
+    for (int d = lane; d < hd; d += 32) {
         float v = 0.0f;
         for (int s = 0; s < splits; ++s) v += to_float<TI>(src[(size_t)s * split_stride + d]);
         v *= rs;
@@ -67,14 +73,21 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
     }
     const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
     if (!is_q && !is_k) {
-        // v head: copy
+        // v head: copy, or blend with the step's first values
         if (!slot_mapping) return;
         const int slot = slot_mapping[t];
         if (slot < 0) return;
         const int h = head - HQ - HKV;
-        TKV* dst = v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D;
+        TKV* dst = v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * DV;
+        float* first = v_first ? v_first + ((size_t)t * HKV + h) * DV : nullptr;
+        const float lam = v_mode == 2 ? *v_lambda : 0.0f;
         __syncwarp();
-        for (int d = lane; d < D; d += 32) dst[d] = from_float<TKV>(row[d]);
+        for (int d = lane; d < DV; d += 32) {
+            float v = row[d];
+            if (v_mode == 1) first[d] = v;
+            else if (v_mode == 2) v = (1.0f - lam) * v + lam * first[d];
+            dst[d] = from_float<TKV>(v);
+        }
         return;
     }
     if (w) {
@@ -370,11 +383,15 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
                                        const int32_t* slot_mapping, void* q_out, int q_dtype, void* k_base,
                                        void* v_base, int kv_dtype, long long page_stride, int page_size, int T,
                                        int HQ, int HKV, int D, int interleaved, const float* row_sumsq, int row_chunks,
-                                       int row_width, float row_eps, cudaStream_t stream) {
+                                       int row_width, float row_eps, int DV, float* v_first, const float* v_lambda, int v_mode,
+                                       cudaStream_t stream) {
     if (!qkv || !positions || !q_out || T < 0 || HQ < 1 || HKV < 0 || D < 2 || splits < 1 || !valid_dtype(qkv_dtype) ||
         !valid_dtype(q_dtype) || !valid_dtype(kv_dtype))
         return fail(PH_ERR_ARG, "qk_norm_rope: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
-    if (D > MAX_D) return fail(PH_ERR_UNSUPPORTED, "qk_norm_rope: head_dim %d exceeds the supported %d", D, MAX_D);
+    if (DV <= 0) DV = D;
+    if (D > MAX_D || DV > MAX_D) return fail(PH_ERR_UNSUPPORTED, "qk_norm_rope: head_dim %d / %d exceeds the supported %d", D, DV, MAX_D);
+    if (v_mode < 0 || v_mode > 2 || (v_mode && !v_first) || (v_mode == 2 && !v_lambda))
+        return fail(PH_ERR_ARG, "qk_norm_rope: value mixing needs the step's first values (and its factor when it blends)");
     if (cos_sin && (n_rot < 2 || n_rot > D || (n_rot & 1) || max_pos < 1))
         return fail(PH_ERR_ARG, "qk_norm_rope: rotary width %d must be even and at most head_dim %d", n_rot, D);
     if (slot_mapping && (!k_base || !v_base || page_size < 1))
@@ -383,7 +400,7 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
     if (T == 0) return PH_OK;
     const RowFactor rf = {row_sumsq, row_chunks, row_width, row_eps};
     dim3 grid(T, (HQ + 2 * HKV + WARPS - 1) / WARPS);
-    const bool fast = D == 128 && (!cos_sin || (n_rot == 128 && !interleaved)) && split_stride % 4 == 0 &&
+    const bool fast = D == 128 && DV == D && v_mode == 0 && (!cos_sin || (n_rot == 128 && !interleaved)) && split_stride % 4 == 0 &&
                       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)bias |
                         (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
     if (fast) {
@@ -409,7 +426,8 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
 #define LAUNCH(TI, TQ, TKV)                                                                                       \
     qk_norm_rope_kernel<TI, TQ, TKV><<<grid, WARPS * 32, 0, stream>>>(                                            \
         (const TI*)qkv, splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, n_rot, max_pos, positions,  \
-        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, interleaved, rf)
+        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, interleaved, rf, DV,     \
+        v_first, v_lambda, v_mode)
     PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH(TI, TQ, TKV))));
 #undef LAUNCH
     return check_launch("qk_norm_rope");

@@ -1,6 +1,7 @@
 #include "engine.h"
 
 #include <algorithm>
+#include <cmath>
 #include <set>
 
 #include "../weights/weights.h"
@@ -253,14 +254,32 @@ Tensor Engine::forward(StepContext& ctx, const int32_t* want_rows, int n_want) {
             const size_t n = (size_t)stream.pending.splits * T * E;
             std::vector<uint8_t> raw(n * dtype_size(p.dtype));
             QE_CUDA(cudaMemcpy(raw.data(), p.data, raw.size(), cudaMemcpyDeviceToHost));
+            std::vector<float> add((size_t)T * E, 0.0f);
             for (int s = 0; s < stream.pending.splits; s++)
                 for (size_t i = 0; i < (size_t)T * E; i++) {
                     const size_t j = (size_t)s * T * E + i;
                     float v;
                     if (p.dtype == DType::F32) memcpy(&v, raw.data() + 4 * j, 4);
                     else { uint16_t h; memcpy(&h, raw.data() + 2 * j, 2); v = bf16_to_f32(h); }
-                    x[i] += v;
+                    add[i] += v;
                 }
+            // an addend's transform (a norm over its rows, then a factor), as the kernel that folds it in applies it
+            const AddendTransform& tr = stream.pending.transform;
+            if (tr.weight) {
+                std::vector<float> w(E), b(E, 0.0f);
+                QE_CUDA(cudaMemcpy(w.data(), tr.weight, (size_t)E * 4, cudaMemcpyDeviceToHost));
+                if (tr.bias) QE_CUDA(cudaMemcpy(b.data(), tr.bias, (size_t)E * 4, cudaMemcpyDeviceToHost));
+                for (int t = 0; t < T; t++) {
+                    float* row = add.data() + (size_t)t * E;
+                    double mean = 0.0, var = 0.0;
+                    for (int i = 0; i < E; i++) mean += row[i];
+                    mean /= E;
+                    for (int i = 0; i < E; i++) var += (row[i] - mean) * (row[i] - mean);
+                    const double inv = 1.0 / std::sqrt(var / E + tr.eps);
+                    for (int i = 0; i < E; i++) row[i] = (float)((row[i] - mean) * inv * w[i] + b[i]);
+                }
+            }
+            for (size_t i = 0; i < (size_t)T * E; i++) x[i] += tr.factor * add[i];
         }
         layer_dump_(entry, x.data(), T, E);
     };

@@ -156,6 +156,16 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_sample_chain", g_core.sample_chain);
     bind(h, "core", "ph_sample_chain_max_k", g_core.sample_chain_max_k);
     bind(h, "core", "ph_random_fill", g_core.random_fill);
+    bind(h, "core", "ph_add_layernorm", g_core.add_layernorm);
+    bind(h, "core", "ph_embed_gather_scaled", g_core.embed_gather_scaled);
+    bind(h, "core", "ph_glu", g_core.glu);
+    bind(h, "core", "ph_causal_conv_silu", g_core.causal_conv_silu);
+    bind(h, "core", "ph_selective_scan", g_core.selective_scan);
+    bind(h, "core", "ph_route_topk", g_core.route_topk);
+    bind(h, "core", "ph_route_max_tiles", g_core.route_max_tiles);
+    bind(h, "core", "ph_route_sort", g_core.route_sort);
+    bind(h, "core", "ph_gemm_grouped", g_core.gemm_grouped);
+    bind(h, "core", "ph_route_combine", g_core.route_combine);
     bind(h, "core", "ph_core_last_error", g_core.last_error);
     g_core_ok = true;
     return g_core;

@@ -95,10 +95,11 @@ struct CoreKernels {
     int (*cast)(const void*, int, void*, int, long long, cudaStream_t);
     int (*qk_norm_rope_kv_write)(const void*, int, int, long long, const float*, const float*, const float*, float,
                                  const float*, int, int, const int32_t*, const int32_t*, void*, int, void*, void*, int,
-                                 long long, int, int, int, int, int, int, const float*, int, int, float, cudaStream_t);
+                                 long long, int, int, int, int, int, int, const float*, int, int, float, int, float*,
+                                 const float*, int, cudaStream_t);
     int (*add_weight_sumsq)(float*, const void*, int, int, long long, const float*, int, int, void*, int, float*, int, cudaStream_t);
     int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
-                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, cudaStream_t);
+                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, cudaStream_t);
     int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
     int (*argmax)(const float*, int, int, int32_t*, void*, long long, cudaStream_t);   // several CTAs per row, with scratch
     long long (*argmax_scratch_bytes)(int);
@@ -106,6 +107,25 @@ struct CoreKernels {
     int (*sample_chain)(const float*, int, int, const void*, int32_t*, cudaStream_t);
     int (*sample_chain_max_k)(void);
     int (*random_fill)(void*, int, long long, unsigned long long, int, double, double, cudaStream_t);
+    // layer norm with the residual add and a transform of the addend in front; an embedding gather with a factor
+    int (*add_layernorm)(float*, const void*, int, int, long long, const float*, const float*, float, float, const float*,
+                         const float*, float, const int32_t*, int, int, void*, int, int, cudaStream_t);
+    int (*embed_gather_scaled)(const void*, int, const int32_t*, float*, int, int, int, float, cudaStream_t);
+    // gated activations by kind (0 silu, 1 clamped swish with alpha, limit, shift)
+    int (*glu)(const void*, int, int, long long, void*, int, int, int, int, float, float, float, cudaStream_t);
+    // selective state-space mixer: convolution + silu, and the scan
+    int (*causal_conv_silu)(const void*, int, long long, int, const float*, const float*, int, const float*, long long, long long,
+                            const int32_t*, const int32_t*, const int32_t*, void*, int, int, cudaStream_t);
+    int (*selective_scan)(const void*, const float*, const float*, const void*, long long, int, int, int, const float*,
+                          const float*, const void*, long long, int, int, float*, long long, const int32_t*, const int32_t*, int,
+                          void*, int, cudaStream_t);
+    // routing: top-k with softmax over the chosen, sort by expert, products by expert, weighted sum
+    int (*route_topk)(const float*, const float*, int, int, int, int32_t*, float*, cudaStream_t);
+    int (*route_max_tiles)(int, int);
+    int (*route_sort)(const int32_t*, int, int, int32_t*, int32_t*, int32_t*, int, int32_t*, cudaStream_t);
+    int (*gemm_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
+                        cudaStream_t);
+    int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, cudaStream_t);
     const char* (*last_error)(void);
 };
 struct FlashKernels {

@@ -8,6 +8,11 @@
 // src/attention.cpp:139-288 (host side; scale at :197), src/attention.h:73 (window),
 // src/inference.cpp:623-646 (tensors and shapes).
 //
+// Options of other designs: values of another width than keys ("value_dim"; o_proj then reads num_heads * value_dim),
+// and value mixing across layers ("value_mix": "first" | "blend"): the first such layer of a model leaves its v for
+// every token of the step, the later ones cache and attend over v <- (1 - lambda) v + lambda v_first, with lambda a
+// scalar tensor of their own ("value_mix_factor").
+//
 // K and V are written to pages before attention runs, and attention reads everything, the current step's keys
 // included, from pages: a whole prompt, a portion and a decoded token are one algorithm per kernel.
 //
@@ -104,9 +109,10 @@ void add_tiles(StepPlan& plan, int rows, const std::string& name) {
 }
 }  // namespace
 
-// params: hidden_size, num_heads, num_kv_heads, head_dim, qk_norm_eps (null: no q/k norm), bias, position
-// (a PartSpec as {kind, params}, or null), window (null: all positions), scale (null: 1/sqrt(head_dim)),
-// names{q_proj, k_proj, v_proj, o_proj, q_norm, k_norm, q_bias, k_bias, v_bias}.
+// params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim (null: head_dim), qk_norm_eps (null: no q/k norm),
+// bias, position (a PartSpec as {kind, params}, or null), window (null: all positions), scale (null:
+// 1/sqrt(head_dim)), value_mix (null | "first" | "blend"),
+// names{q_proj, k_proj, v_proj, o_proj, q_norm, k_norm, q_bias, k_bias, v_bias, value_mix_factor}.
 class Attention : public Mixer {
 public:
     Attention(const Json& p, BuildContext& b) : Mixer(p, b) {
@@ -114,6 +120,11 @@ public:
         heads_ = (int)p.at("num_heads").as_int();
         kv_heads_ = (int)p.at("num_kv_heads").as_int();
         head_dim_ = (int)p.at("head_dim").as_int();
+        value_dim_ = (int)p.get_int("value_dim", head_dim_);
+        if (value_dim_ < 1) throw ConfigError("attention: value_dim must be positive");
+        const std::string mix = p.get_string("value_mix", "");
+        if (!mix.empty() && mix != "first" && mix != "blend") throw ConfigError("attention: value_mix is 'first' or 'blend', got '" + mix + "'");
+        value_mix_ = mix == "first" ? 1 : mix == "blend" ? 2 : 0;
         if (heads_ < 1 || kv_heads_ < 1 || heads_ % kv_heads_)
             throw ConfigError(std::to_string(heads_) + " query heads are not a multiple of " + std::to_string(kv_heads_) + " kv heads");
         const Json* eps = p.find("qk_norm_eps");
@@ -137,14 +148,17 @@ public:
         attention_ = b.options.get_string("attention", "auto");
         q_width_ = (int64_t)heads_ * head_dim_;
         kv_width_ = (int64_t)kv_heads_ * head_dim_;
+        v_width_ = (int64_t)kv_heads_ * value_dim_;
+        o_width_ = (int64_t)heads_ * value_dim_;
     }
 
     // ---- weights ----------------------------------------------------------------------------------------------
     std::vector<TensorSpec> tensor_specs() const override {
         std::vector<TensorSpec> s = {{name_of("q_proj"), {q_width_, hidden_}, Role::Matrix, Init::Normal},
                                      {name_of("k_proj"), {kv_width_, hidden_}, Role::Matrix, Init::Normal},
-                                     {name_of("v_proj"), {kv_width_, hidden_}, Role::Matrix, Init::Normal},
-                                     {name_of("o_proj"), {hidden_, q_width_}, Role::Matrix, Init::Normal}};
+                                     {name_of("v_proj"), {v_width_, hidden_}, Role::Matrix, Init::Normal},
+                                     {name_of("o_proj"), {hidden_, o_width_}, Role::Matrix, Init::Normal}};
+        if (value_mix_ == 2) s.push_back({name_of("value_mix_factor"), {}, Role::Vector, Init::Normal});
         if (has_norm_) {
             s.push_back({name_of("q_norm"), {head_dim_}, Role::Vector, Init::Scale});
             s.push_back({name_of("k_norm"), {head_dim_}, Role::Vector, Init::Scale});
@@ -152,7 +166,7 @@ public:
         if (has_bias_) {
             s.push_back({name_of("q_bias"), {q_width_}, Role::Vector, Init::Normal});
             s.push_back({name_of("k_bias"), {kv_width_}, Role::Vector, Init::Normal});
-            s.push_back({name_of("v_bias"), {kv_width_}, Role::Vector, Init::Normal});
+            s.push_back({name_of("v_bias"), {v_width_}, Role::Vector, Init::Normal});
         }
         return s;
     }
@@ -162,7 +176,7 @@ public:
         Tensor parts[3] = {src.fetch(name_of("q_proj")), src.fetch(name_of("k_proj")), src.fetch(name_of("v_proj"))};
         if (parts[0].dtype != parts[1].dtype || parts[0].dtype != parts[2].dtype)
             throw WeightError(name_of("q_proj") + ", " + name_of("k_proj") + " and " + name_of("v_proj") + " are stored in different precisions");
-        Tensor qkv = src.arena().alloc(parts[0].dtype, {q_width_ + 2 * kv_width_, hidden_});
+        Tensor qkv = src.arena().alloc(parts[0].dtype, {q_width_ + kv_width_ + v_width_, hidden_});
         size_t off = 0;
         for (Tensor& t : parts) {
             QE_CUDA(cudaMemcpyAsync(static_cast<char*>(qkv.data) + off, t.data, t.bytes(), cudaMemcpyDeviceToDevice, src.stream()));
@@ -170,7 +184,7 @@ public:
         }
         if (has_bias_) {
             Tensor b[3] = {src.fetch(name_of("q_bias")), src.fetch(name_of("k_bias")), src.fetch(name_of("v_bias"))};
-            bias_ = src.arena().alloc(DType::F32, {q_width_ + 2 * kv_width_});
+            bias_ = src.arena().alloc(DType::F32, {q_width_ + kv_width_ + v_width_});
             off = 0;
             for (Tensor& t : b) {
                 QE_CUDA(cudaMemcpyAsync(static_cast<char*>(bias_.data) + off, t.data, t.bytes(), cudaMemcpyDeviceToDevice, src.stream()));
@@ -188,6 +202,7 @@ public:
             q_norm_ = src.fetch(name_of("q_norm"));
             k_norm_ = src.fetch(name_of("k_norm"));
         }
+        if (value_mix_ == 2) mix_factor_ = src.fetch(name_of("value_mix_factor"));
         if (position_) {
             position_->bind(src);
             table_ = position_->rotation_table();
@@ -200,6 +215,11 @@ public:
         if (use_flash()) libs.push_back("flash");
         return libs;
     }
+    std::vector<std::string> ignored_tensors() const override {
+        // the first mixing layer has nothing to blend with; a factor stored for it is not read
+        if (value_mix_ == 1 && names_.count("value_mix_factor")) return {name_of("value_mix_factor")};
+        return {};
+    }
     std::vector<Part*> children() override { return position_ ? std::vector<Part*>{position_.get()} : std::vector<Part*>{}; }
     // rows per tile of the products for many tokens (the tcgen05 pair kernel): a scheduler may end a step there
     int preferred_row_multiple() const override { return (qkv_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
@@ -207,7 +227,7 @@ public:
     bool use_flash() const {
         if (compute_dtype != DType::BF16 || attention_ == "generic") return false;
         const int group = heads_ / kv_heads_;
-        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && group >= 1 && group <= 16;
+        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16;
         if (!ok && attention_ == "flash")
             throw KernelError("the flash attention kernels do not take head_dim " + std::to_string(head_dim_) + " with " +
                               std::to_string(group) + " query heads per kv head");
@@ -215,7 +235,7 @@ public:
     }
 
     // ---- cache and step metadata ------------------------------------------------------------------------------
-    CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_); }
+    CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_); }
 
     void prepare_step(StepPlan& plan) override {
         if (!use_flash()) return;
@@ -248,21 +268,25 @@ public:
         const Linear& proj = cache.writable ? qkv_proj_ : q_only_proj_;
         // rows without their factor (RowScale): the product's epilogue applies it where it can, else the kernel behind it
         const bool scale_in_product = ctx.row_scale.defined() && proj.applies_row_scale(T, dt, false, true);
+        if (!cache.writable && value_mix_) throw Error(kInvalidState, "a layer that mixes values writes a cache of its own");
         Addend qkv = proj(x, ctx, "qkv", dt, T, true, false, nullptr, scale_in_product ? &ctx.row_scale : nullptr);
+        // the values of the first mixing layer, per token of the step: written by that layer, read by the later ones
+        float* v_first = value_mix_ ? ws.get("attention.v_first", {T, v_width_}, DType::F32).as<float>() : nullptr;
         const RowScale later = scale_in_product ? RowScale() : ctx.row_scale;
         const int kv_heads_written = cache.writable ? kv_heads_ : 0;
         Tensor q = ws.get("q", {T, heads_, head_dim_}, dt);
         const int column = position_ ? position_->position_column() : 0;
         const int32_t* positions = ctx.position_column(column);
         QE_LAUNCH(core, core.qk_norm_rope_kv_write(
-            qkv.tensor.data, qkv.tensor.code(), qkv.splits, (long long)T * (q_width_ + 2 * (int64_t)kv_heads_written * head_dim_),
+            qkv.tensor.data, qkv.tensor.code(), qkv.splits, (long long)T * (q_width_ + (int64_t)kv_heads_written * (head_dim_ + value_dim_)),
             bias_.defined() ? bias_.as<float>() : nullptr, has_norm_ ? q_norm_.as<float>() : nullptr,
             has_norm_ ? k_norm_.as<float>() : nullptr, (float)eps_, table_.defined() ? table_.as<float>() : nullptr,
             position_ ? position_->n_rot() : 0, table_.defined() ? (int)table_.shape[0] : 0, positions,
             cache.writable ? g.slot_mapping : nullptr, q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype,
             cache.page_stride, cache.page_size, T, heads_, kv_heads_written, head_dim_,
-            position_ && position_->interleaved() ? 1 : 0, later.sumsq, later.chunks, later.width, later.eps, ctx.stream));
-        Tensor out = ws.get("attn_out", {T, q_width_}, dt);
+            position_ && position_->interleaved() ? 1 : 0, later.sumsq, later.chunks, later.width, later.eps, value_dim_, v_first,
+            mix_factor_.defined() ? mix_factor_.as<float>() : nullptr, value_mix_, ctx.stream));
+        Tensor out = ws.get("attn_out", {T, o_width_}, dt);
         const int32_t* abs_positions = ctx.position_column(0);       // the mask always follows the index in the request
         if (use_flash()) {
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
@@ -270,7 +294,8 @@ public:
         } else {
             QE_LAUNCH(core, core.attention_generic(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                    cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
-                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, ctx.stream));
+                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_,
+                                                   ctx.stream));
         }
         return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
@@ -324,14 +349,14 @@ private:
                                   splits, window_, (float)scale_, ctx.stream));
     }
 
-    int64_t hidden_, q_width_, kv_width_;
-    int heads_, kv_heads_, head_dim_, window_;
+    int64_t hidden_, q_width_, kv_width_, v_width_, o_width_;
+    int heads_, kv_heads_, head_dim_, value_dim_, window_, value_mix_ = 0;
     bool has_norm_, has_bias_;
     double eps_, scale_;
     std::string gemm_, attention_;
     std::shared_ptr<PositionEncoding> position_;
     Linear qkv_proj_, q_only_proj_, o_proj_;
-    Tensor q_norm_, k_norm_, bias_, table_;
+    Tensor q_norm_, k_norm_, bias_, table_, mix_factor_;
 };
 
 void register_mixer_parts() {

@@ -3,6 +3,13 @@
 // pre_norm: x += mixer(norm1(x)); x += feed_forward(norm2(x)), with each addition folded into the norm that
 // follows it (the reference fuses them the same way: src/qwen_model.cpp:1175-1187, 1248, 1260).  Sub-parts by
 // name: mixer_norm, mixer, feed_forward_norm, feed_forward.
+//
+// sandwich_norm: x += m * post_norm(mixer(norm1(x))); x += m * post_norm2(feed_forward(norm2(x))), a norm in front of
+// and behind each part and a factor m on what is added (layer param "residual_factor", default 1).  The norm behind
+// a part and the factor travel with the part's addend as its transform, and the next norm's kernel applies them in
+// the pass in which it adds and norms, so a layer still launches two norm kernels.  Sub-parts by name: mixer_norm,
+// mixer, mixer_post_norm, and, unless the layer has no feed-forward, feed_forward_norm, feed_forward,
+// feed_forward_post_norm.
 #include "parts.h"
 
 namespace qe {
@@ -51,7 +58,54 @@ private:
     std::shared_ptr<FeedForward> ff_;
 };
 
+class SandwichNormBlock : public Arrangement {
+public:
+    SandwichNormBlock(const LayerSpec& layer, BuildContext& build) {
+        factor_ = (float)layer.params.get_double("residual_factor", 1.0);
+        mixer_norm_ = make_part_as<Norm>("norm", layer.part("mixer_norm"), build);
+        mixer_ = make_part_as<Mixer>("mixer", layer.part("mixer"), build);
+        mixer_post_ = make_part_as<Norm>("norm", layer.part("mixer_post_norm"), build);
+        if (layer.has("feed_forward")) {
+            ff_norm_ = make_part_as<Norm>("norm", layer.part("feed_forward_norm"), build);
+            ff_ = make_part_as<FeedForward>("feed_forward", layer.part("feed_forward"), build);
+            ff_post_ = make_part_as<Norm>("norm", layer.part("feed_forward_post_norm"), build);
+        }
+    }
+    std::vector<Part*> parts() override {
+        std::vector<Part*> p = {mixer_norm_.get(), mixer_.get(), mixer_post_.get()};
+        if (ff_) { p.push_back(ff_norm_.get()); p.push_back(ff_.get()); p.push_back(ff_post_.get()); }
+        return p;
+    }
+    CacheNeed cache_need() const override { return mixer_->cache_need(); }
+    void forward(ResidualStream& stream, StepContext& ctx, const CacheView& cache) override {
+        // what a part gives is normed before it is added: no product adds into the residual behind this block's back,
+        // and no norm's work is handed to a product
+        ctx.residual = nullptr;
+        ctx.residual_width = 0;
+        ctx.row_scale = RowScale();
+        ctx.norm_ahead = NormAhead();
+        Tensor xn = mixer_norm_->forward(stream, ctx);
+        Addend mixed = mixer_->forward(xn, ctx, cache);
+        if (!mixed.tensor.defined()) throw Error(kInvalidState, "sandwich_norm: the mixer added into the residual itself");
+        mixed.transform = mixer_post_->as_transform(factor_);
+        stream.add(std::move(mixed));
+        if (!ff_) return;
+        xn = ff_norm_->forward(stream, ctx);
+        Addend fed = ff_->forward(xn, ctx);
+        if (!fed.tensor.defined()) throw Error(kInvalidState, "sandwich_norm: the feed-forward added into the residual itself");
+        fed.transform = ff_post_->as_transform(factor_);
+        stream.add(std::move(fed));
+    }
+private:
+    float factor_ = 1.0f;
+    std::shared_ptr<Norm> mixer_norm_, mixer_post_, ff_norm_, ff_post_;
+    std::shared_ptr<Mixer> mixer_;
+    std::shared_ptr<FeedForward> ff_;
+};
+
 void register_norm_parts();
+void register_routed_parts();
+void register_state_space_parts();
 void register_position_parts();
 void register_mixer_parts();
 void register_feed_forward_parts();
@@ -66,6 +120,11 @@ void register_builtin_parts() {
     register_mixer_parts();
     register_feed_forward_parts();
     register_embedding_parts();
+    register_routed_parts();
+    register_state_space_parts();
+    register_arrangement("sandwich_norm", [](const LayerSpec& layer, BuildContext& build) {
+        return std::unique_ptr<Arrangement>(new SandwichNormBlock(layer, build));
+    });
     register_arrangement("pre_norm", [](const LayerSpec& layer, BuildContext& build) {
         return std::unique_ptr<Arrangement>(new PreNormBlock(layer, build));
     });

@@ -1,6 +1,6 @@
 // Token embedding and output head.
 //
-// x[t] = table[token[t]] without scaling (src/qwen_model.cpp:1234-1244); logits = W_out xn for the rows that are
+// x[t] = table[token[t]] (src/qwen_model.cpp:1234-1244), times `scale` where a design has one; logits = W_out xn for the rows that are
 // asked for only (src/qwen_model.cpp:1421-1486).  A tied head shares the embedding table
 // (src/inference.cpp:1392-1396).
 #include "linear.h"
@@ -8,21 +8,26 @@
 
 namespace qe {
 
-// params: vocab_size, hidden_size, names{weight}.
+// params: vocab_size, hidden_size, scale (default 1), names{weight}.
 class TokenEmbedding : public Embedding {
 public:
     TokenEmbedding(const Json& p, BuildContext& b)
-        : Embedding(p, b), vocab_(p.at("vocab_size").as_int()), hidden_(p.at("hidden_size").as_int()) {}
+        : Embedding(p, b), vocab_(p.at("vocab_size").as_int()), hidden_(p.at("hidden_size").as_int()), scale_(p.get_double("scale", 1.0)) {}
     std::vector<TensorSpec> tensor_specs() const override { return {{name_of("weight"), {vocab_, hidden_}, Role::Matrix, Init::Normal}}; }
     void bind(WeightSource& src) override { table_ = src.fetch(name_of("weight")); }
     Tensor forward(StepContext& ctx) override {
         Tensor x = ctx.workspace->get("residual", {ctx.T, hidden_}, DType::F32);
         const CoreKernels& k = core_kernels();
-        QE_LAUNCH(k, k.embed_gather(table_.data, table_.code(), ctx.token_ids, x.as<float>(), ctx.T, (int)hidden_, (int)vocab_, ctx.stream));
+        if (scale_ == 1.0)
+            QE_LAUNCH(k, k.embed_gather(table_.data, table_.code(), ctx.token_ids, x.as<float>(), ctx.T, (int)hidden_, (int)vocab_, ctx.stream));
+        else
+            QE_LAUNCH(k, k.embed_gather_scaled(table_.data, table_.code(), ctx.token_ids, x.as<float>(), ctx.T, (int)hidden_, (int)vocab_,
+                                               (float)scale_, ctx.stream));
         return x;
     }
 private:
     int64_t vocab_, hidden_;
+    double scale_;
     Tensor table_;
 };
 

@@ -1,18 +1,21 @@
-// SwiGLU feed-forward: y = Wd (silu(Wg x) * (Wu x)).
+// Gated feed-forward: y = Wd act(Wg x, Wu x), with act(g, u) = silu(g) * u (SwiGLU) unless the part is given another
+// gate: "clamped_swish" is g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
 //
 // Reference: src/qwen_model.cpp:1170-1189 (gate and up as one grouped product, the activation, down),
 // src/gpu_ops.hip:103-114 (silu(g) * u with g / (1 + exp(-g))).
+#include "gate.h"
 #include "linear.h"
 #include "parts.h"
 
 namespace qe {
 
-// params: hidden_size, intermediate_size, names{gate_proj, up_proj, down_proj}.
+// params: hidden_size, intermediate_size, activation (null: silu; or {"kind": "clamped_swish", "alpha", "limit",
+// "shift"}), names{gate_proj, up_proj, down_proj}.
 class SwiGLU : public FeedForward {
 public:
     SwiGLU(const Json& p, BuildContext& b)
         : FeedForward(p, b), hidden_(p.at("hidden_size").as_int()), inter_(p.at("intermediate_size").as_int()),
-          gemm_(b.options.get_string("gemm", "auto")) {}
+          gemm_(b.options.get_string("gemm", "auto")), gate_(GateSpec::read(p)) {}
 
     std::vector<TensorSpec> tensor_specs() const override {
         return {{name_of("gate_proj"), {inter_, hidden_}, Role::Matrix, Init::Normal},
@@ -43,19 +46,24 @@ public:
 
     // bfloat16: the gate/up product's epilogue applies the norm's factor per row before the activation
     bool takes_unscaled_rows(const StepContext& ctx) const override {
-        return compute_dtype == DType::BF16 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
+        return compute_dtype == DType::BF16 && gate_.kind == 0 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
     }
 
     Addend forward(const Tensor& x, StepContext& ctx) override {
         const int T = ctx.T;
-        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, true, nullptr, &ctx.row_scale);
+        // the products' own epilogue knows the silu gate; any other gate is a kernel behind the product
+        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, gate_.kind == 0, nullptr, &ctx.row_scale);
         Tensor act;
         if (gu.activated) act = gu.tensor;
         else {
             act = ctx.workspace->get("ff_act", {T, inter_}, compute_dtype);
             const CoreKernels& k = core_kernels();
-            QE_LAUNCH(k, k.swiglu(gu.tensor.data, gu.tensor.code(), gu.splits, (long long)T * 2 * inter_, act.data, act.code(), T,
-                                  (int)inter_, ctx.stream));
+            if (gate_.kind == 0)
+                QE_LAUNCH(k, k.swiglu(gu.tensor.data, gu.tensor.code(), gu.splits, (long long)T * 2 * inter_, act.data, act.code(), T,
+                                      (int)inter_, ctx.stream));
+            else
+                QE_LAUNCH(k, k.glu(gu.tensor.data, gu.tensor.code(), gu.splits, (long long)T * 2 * inter_, act.data, act.code(), T,
+                                   (int)inter_, gate_.kind, gate_.alpha, gate_.limit, gate_.shift, ctx.stream));
         }
         return down_(act, ctx, "ff_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
@@ -63,6 +71,7 @@ public:
 private:
     int64_t hidden_, inter_;
     std::string gemm_;
+    GateSpec gate_;
     Linear gate_up_, down_;
 };
 

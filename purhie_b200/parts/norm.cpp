@@ -1,10 +1,29 @@
-// RMSNorm with the residual add folded in.
+// The norms: RMSNorm and the layer norm with weight and bias, each with the residual add folded in.
 //
 // y = v * rsqrt(mean(v^2) + eps) * w, v = x + pending addend; the weight multiplies after normalising (plain w,
 // not 1 + w).  Reference: src/gpu_ops.hip:24-56 (add + norm in one kernel), src/qwen_ops.cpp:8-13.
 #include "parts.h"
 
 namespace qe {
+
+AddendTransform Norm::as_transform(float) const {
+    throw ConfigError("this norm cannot be applied to an addend on its way into the residual");
+}
+
+namespace {
+// x += factor * norm(addend) for a pending addend with a transform, by the kernel that knows transforms; afterwards
+// the stream has nothing pending.  For norms whose own kernel does not know them.
+void fold_transformed(ResidualStream& stream, StepContext& ctx) {
+    if (!stream.has_pending || !stream.pending.transform.defined()) return;
+    const Addend& a = stream.pending;
+    const int64_t E = stream.x.shape[1];
+    const CoreKernels& k = core_kernels();
+    QE_LAUNCH(k, k.add_layernorm(stream.x.as<float>(), a.tensor.data, a.tensor.code(), a.splits, (long long)ctx.T * E,
+                                 a.transform.weight, a.transform.bias, a.transform.eps, a.transform.factor, nullptr, nullptr, 0.0f,
+                                 nullptr, ctx.T, (int)E, nullptr, 0, 1, ctx.stream));
+    stream.clear();
+}
+}  // namespace
 
 // params: size, eps, names{weight}.
 class RMSNorm : public Norm {
@@ -17,6 +36,7 @@ public:
 
     Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
         const int n = rows ? n_rows : ctx.T;
+        fold_transformed(stream, ctx);
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
@@ -39,6 +59,7 @@ public:
             return rows;
         }
         if (compute_dtype != DType::BF16 || size_ % 4) return forward(stream, ctx, nullptr, 0);
+        fold_transformed(stream, ctx);
         constexpr int kChunk = 512;                                   // columns per CTA of the kernel
         const int chunks = (int)((size_ + kChunk - 1) / kChunk);
         Tensor out = ctx.workspace->get("normed", {ctx.T, size_}, compute_dtype);
@@ -66,8 +87,50 @@ private:
     Tensor weight_;
 };
 
+// Layer norm with weight and bias: y = (v - mean(v)) / sqrt(var(v) + eps) * w + b, var the mean of the squared
+// deviations, v = x + the pending addend.  A pending addend may carry a transform (a norm of this kind over the
+// addend's own rows and a factor): the one kernel applies it, adds, and norms the sum, which is all a layer of the
+// form x <- x + m * norm_b(f(norm_a(x))) needs between two parts.
+// params: size, eps, names{weight, bias}.
+class LayerNorm : public Norm {
+public:
+    LayerNorm(const Json& p, BuildContext& b) : Norm(p, b), size_(p.at("size").as_int()), eps_(p.at("eps").as_double()) {
+        if (size_ < 1 || !(eps_ >= 0)) throw ConfigError("layernorm: size must be positive and eps >= 0");
+    }
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("weight"), {size_}, Role::Vector, Init::Scale}, {name_of("bias"), {size_}, Role::Vector, Init::Normal}};
+    }
+    void bind(WeightSource& src) override {
+        weight_ = src.fetch(name_of("weight"));
+        bias_ = src.fetch(name_of("bias"));
+    }
+    Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
+        const int n = rows ? n_rows : ctx.T;
+        Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
+        const CoreKernels& k = core_kernels();
+        const Addend* a = stream.has_pending ? &stream.pending : nullptr;
+        QE_LAUNCH(k, k.add_layernorm(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
+                                     a ? (long long)ctx.T * size_ : 0, a ? a->transform.weight : nullptr, a ? a->transform.bias : nullptr,
+                                     a ? a->transform.eps : 0.0f, a ? a->transform.factor : 1.0f, weight_.as<float>(),
+                                     bias_.as<float>(), (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1,
+                                     ctx.stream));
+        if (!rows) stream.clear();
+        return out;
+    }
+    AddendTransform as_transform(float factor) const override {
+        AddendTransform t;
+        t.weight = weight_.as<float>(); t.bias = bias_.as<float>(); t.eps = (float)eps_; t.factor = factor;
+        return t;
+    }
+private:
+    int64_t size_;
+    double eps_;
+    Tensor weight_, bias_;
+};
+
 void register_norm_parts() {
     register_part("norm", "rmsnorm", [](const Json& p, BuildContext& b) { return std::make_shared<RMSNorm>(p, b); });
+    register_part("norm", "layernorm", [](const Json& p, BuildContext& b) { return std::make_shared<LayerNorm>(p, b); });
 }
 
 }  // namespace qe

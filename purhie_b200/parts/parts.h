@@ -100,6 +100,7 @@ struct PartSpec {
 
 struct LayerSpec {
     std::string arrangement = "pre_norm";
+    Json params = Json::object();                                 // constants of the arrangement itself (a residual factor, say)
     std::vector<std::pair<std::string, PartSpec>> parts;          // sub-parts by the names the arrangement reads
     const PartSpec& part(const std::string& name) const {
         for (const auto& p : parts) if (p.first == name) return p.second;
@@ -145,10 +146,22 @@ struct CacheView {
     Tensor state;                            // [max_requests, *state_shape]
 };
 
+// What is done to each row of an addend on its way into the residual: a layer norm over the row with weight and bias
+// (weight null: none), then a factor.  Whoever folds the addend in applies it (the norm that follows, in the pass it
+// makes over the row anyway), so x <- x + factor * norm(f(...)) costs no launch of its own.
+struct AddendTransform {
+    const float* weight = nullptr;           // [E] float32 on the device
+    const float* bias = nullptr;             // [E] or null
+    float eps = 0.0f;
+    float factor = 1.0f;
+    bool defined() const { return weight != nullptr || factor != 1.0f; }
+};
+
 struct Addend {
     Tensor tensor;                           // [T, E], or [splits, T, E] partial sums; undefined: already added
     int splits = 1;
     bool activated = false;                  // a product whose activation was applied in the kernel's epilogue
+    AddendTransform transform;               // applied to the rows before they are added (see above)
     Addend() : splits(0) {}
     Addend(Tensor t, int s = 1, bool act = false) : tensor(std::move(t)), splits(s), activated(act) {}
 };
@@ -304,6 +317,9 @@ public:
     // What a product in front may do of this norm's work (NormAhead), if forward_unscaled() would pick it up from
     // stream.prepared; a norm that has no such form offers nothing.
     virtual NormAhead offer(const StepContext&) const { return NormAhead(); }
+    // This norm as a transform of an addend (AddendTransform) with the given factor, for a layer that norms what a
+    // part gives before adding it; a norm that has no such form throws.
+    virtual AddendTransform as_transform(float factor) const;
 };
 
 class QE_API PositionEncoding : public Part {
@@ -377,7 +393,8 @@ template <typename T> std::shared_ptr<T> make_part_as(const std::string& family,
     return p;
 }
 
-// Registers the parts this library brings (rmsnorm, rope_neox, attention, swiglu, embedding, lm_head, pre_norm).
+// Registers the parts this library brings (rmsnorm, layernorm, rope_neox, attention, mamba1, swiglu, routed_glu,
+// embedding, lm_head, pre_norm, sandwich_norm).
 QE_API void register_builtin_parts();
 
 }  // namespace qe

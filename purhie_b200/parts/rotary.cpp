@@ -5,6 +5,13 @@
 // precision on the host and stored as float32 cosines and sines.  Reference: src/qwen_ops.cpp:15-24 (double
 // theta), src/attention.hip:225-240 (the device version); base and width: src/inference.cpp:1358-1359; the
 // frequency factors and the interleaved pairing are the reference's knobs of src/attention.h:69, 84-95.
+//
+// Scaling for contexts longer than the trained one ("scaling": {"kind": "yarn", factor, original, fast, slow}): the
+// pair whose wavelength makes t turns over `original` positions is pair(t) = n_rot * ln(original / (2 pi t)) / (2 ln
+// theta); with lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), n_rot - 1) and ramp_i = clamp((i - lo) /
+// max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * ramp_i + f_i * (1 - ramp_i) (fast pairs keep their
+// frequency, slow ones are stretched by the factor), and every cosine and sine is multiplied by 0.1 ln(factor) + 1.
+#include <algorithm>
 #include <cmath>
 
 #include "parts.h"
@@ -12,7 +19,7 @@
 namespace qe {
 
 // params: theta, n_rot, max_position; optional pairing ("half" | "interleaved"), freq_factors [n_rot/2] (each
-// pair's frequency is divided by its factor), position_column.
+// pair's frequency is divided by its factor), scaling (null or {"kind": "yarn", ...} as above), position_column.
 class RotaryTable : public PositionEncoding {
 public:
     RotaryTable(const Json& p, BuildContext& b) : PositionEncoding(p, b) {
@@ -29,6 +36,19 @@ public:
                 for (const Json& v : f->items()) factors_.push_back(v.as_double());
             }
         }
+        if (const Json* sc = p.find("scaling")) {
+            if (!sc->is_null()) {
+                const std::string kind = sc->get_string("kind", "");
+                if (kind != "yarn") throw ConfigError("rotary: scaling of kind '" + kind + "' is not known (yarn is)");
+                yarn_ = true;
+                factor_ = sc->at("factor").as_double();
+                original_ = sc->at("original").as_double();
+                fast_ = sc->at("fast").as_double();
+                slow_ = sc->at("slow").as_double();
+                if (!(factor_ > 0) || !(original_ > 0) || !(fast_ > 0) || !(slow_ > 0) || !(theta_ != 1.0))
+                    throw ConfigError("rotary: yarn scaling needs positive factor, original, fast and slow");
+            }
+        }
     }
     int n_rot() const override { return n_rot_; }
     bool interleaved() const override { return interleaved_; }
@@ -43,11 +63,22 @@ public:
             inv[i] = std::pow(theta_, -2.0 * i / n_rot_);
             if (!factors_.empty()) inv[i] /= factors_[i];
         }
+        double stretch = 1.0;
+        if (yarn_) {
+            const double kPi = 3.14159265358979323846;
+            auto pair_of = [&](double turns) { return n_rot_ * std::log(original_ / (2.0 * kPi * turns)) / (2.0 * std::log(theta_)); };
+            const double lo = std::max(std::floor(pair_of(fast_)), 0.0), hi = std::min(std::ceil(pair_of(slow_)), (double)n_rot_ - 1.0);
+            for (int i = 0; i < half; i++) {
+                const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+                inv[i] = inv[i] / factor_ * ramp + inv[i] * (1.0 - ramp);
+            }
+            stretch = 0.1 * std::log(factor_) + 1.0;
+        }
         for (int64_t pos = 0; pos < max_position_; pos++)
             for (int i = 0; i < half; i++) {
                 const double a = (double)pos * inv[i];
-                host[(size_t)pos * n_rot_ + i] = (float)std::cos(a);
-                host[(size_t)pos * n_rot_ + half + i] = (float)std::sin(a);
+                host[(size_t)pos * n_rot_ + i] = (float)(std::cos(a) * stretch);
+                host[(size_t)pos * n_rot_ + half + i] = (float)(std::sin(a) * stretch);
             }
         table_ = src.arena().alloc(DType::F32, {max_position_, n_rot_});
         QE_CUDA(cudaMemcpy(table_.data, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice));
@@ -59,6 +90,8 @@ private:
     int n_rot_, column_;
     int64_t max_position_;
     bool interleaved_;
+    bool yarn_ = false;
+    double factor_ = 1.0, original_ = 0.0, fast_ = 0.0, slow_ = 0.0;
     std::vector<double> factors_;
     Tensor table_;
 };
