@@ -75,7 +75,8 @@ class TraceRun:
         cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype,
                "--out", self.out_dir, "--max-tokens", str(max_tokens)] + list(extra)
         self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
-        self.vocab = json.load(open(os.path.join(str(model_dir), "config.json")))["vocab_size"]
+        cfg = json.load(open(os.path.join(str(model_dir), "config.json")))
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
 
     def step(self, step, entries, end=()):
         rec = {"step": step, "entries": [{"id": i, "tokens": list(t), "want": list(w)} for i, t, w in entries],

@@ -1,7 +1,7 @@
 """A plain, slow Bozosun forward pass: one whole sequence from position 0, no cache, one function per mechanism.
 
 It shares no code with ``purhie_b200``: it reads ``config.json`` with ``json`` and the weight file by its byte
-layout, and states every equation directly.  Everything runs in float64 unless ``dtype`` says otherwise.
+layout, and states every equation directly.  Everything runs in float64.
 
 The design in short (names of config.json in quotes):
 
@@ -146,7 +146,8 @@ def attention_mixer(h, w, pre, m, shared):
     k = linear(h, w[pre + "k"]).reshape(T, G, D)
     v = linear(h, w[pre + "v"]).reshape(T, G, Dv)
     pos = np.arange(T)
-    q, k = rotate(q, pos, m["rot"]), rotate(k, pos, m["rot"])
+    if m.get("rot"):
+        q, k = rotate(q, pos, m["rot"]), rotate(k, pos, m["rot"])
     if m.get("v_mix"):
         if "v_first" not in shared:
             shared["v_first"] = v
