@@ -8,6 +8,10 @@
 //   gemm_grouped   y[i] = W[expert of i] x[source row of i] for the sorted positions i, tile by tile; float32
 //                  multiply-add on the CUDA cores with k ascending inside one thread (the order of gemm_simple),
 //                  so a row's result depends on neither its place in the batch nor its place among the expert's rows.
+//   gemv_grouped   the same product for a handful of rows per expert (decoding): a warp per output feature streams
+//                  that feature's weight row once, 16 bytes per lane and load, for up to eight rows of the tile at a
+//                  time; a row's sum is taken in one order (lane by lane over k, then a butterfly), whatever else
+//                  the tile holds.  This is weight streaming: its bound is the bytes of the chosen experts.
 //   route_combine  out[t] = sum over the token's choices, in the order of the choices, weight * y[position of (t, j)].
 #include "common.cuh"
 
@@ -151,6 +155,76 @@ __global__ void __launch_bounds__(256) gemm_grouped_kernel(const TX* __restrict_
     }
 }
 
+// eight consecutive elements as floats (16 bytes of bfloat16, 32 of float32)
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(h[i]); v[2 * i + 1] = __high2float(h[i]); }
+}
+
+constexpr int GV_ROWS = 8, GV_WARPS = 8;
+
+// grid (ceil(N / GV_WARPS), tiles); K % 8 == 0 and 16-byte aligned rows (checked by the launcher)
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_grouped_kernel(const TX* __restrict__ x, const int32_t* __restrict__ pair_at,
+                                                                     int pairs_per_row, const TW* __restrict__ w,
+                                                                     const int32_t* __restrict__ tiles, TY* __restrict__ y, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    if (rows == 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    if (n >= N) return;
+    const TW* wr = w + ((size_t)expert * N + n) * K;
+    for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
+        const TX* xr[GV_ROWS];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            const int i = row0 + r0 + (r0 + r < rows ? r : 0);             // rows past the end repeat the first (never stored)
+            xr[r] = x + (size_t)(pair_at ? pair_at[i] / pairs_per_row : i) * K;
+        }
+        float acc[GV_ROWS];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) acc[r] = 0.0f;
+        for (int k = lane * 8; k < K; k += 32 * 8) {
+            float wv[8];
+            load8(wr + k, wv);
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) {
+                if (r0 + r >= rows) continue;                              // the same for the whole block
+                float xv[8];
+                load8(xr[r] + k, xv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[r] = fmaf(xv[j], wv[j], acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            const float total = warp_sum(acc[r]);
+            if (lane == 0 && r0 + r < rows) y[(size_t)(row0 + r0 + r) * N + n] = from_float<TY>(total);
+        }
+    }
+}
+
+// out[i] = x[token of the pair at sorted position i]: the rows of x in the order of the experts
+template <typename TX>
+__global__ void route_gather_kernel(const TX* __restrict__ x, const int32_t* __restrict__ pair_at, int pairs_per_row,
+                                    TX* __restrict__ out, int K, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long i = idx / K;
+    const int k = (int)(idx % K);
+    out[idx] = x[(size_t)(pair_at[i] / pairs_per_row) * K + k];
+}
+
 template <typename TY>
 __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
                                      int top, float* __restrict__ out, int E_out, long long total) {
@@ -205,6 +279,36 @@ PH_EXPORT int ph_gemm_grouped(const void* x, int x_dtype, const int32_t* pair_at
     PH_DISPATCH(x_dtype, TX, PH_DISPATCH(w_dtype, TW, PH_DISPATCH(y_dtype, TY, LAUNCH(TX, TW, TY))));
 #undef LAUNCH
     return check_launch("gemm_grouped");
+}
+
+PH_EXPORT int ph_route_gather(const void* x, int dtype, const int32_t* pair_at, int pairs_per_row, void* out, int R, int K,
+                              cudaStream_t stream) {
+    if (!x || !pair_at || !out || R < 0 || K < 1 || pairs_per_row < 1 || !valid_dtype(dtype))
+        return fail(PH_ERR_ARG, "route_gather: bad arguments (rows %d, K %d)", R, K);
+    const long long total = (long long)R * K;
+    if (total == 0) return PH_OK;
+    PH_DISPATCH(dtype, TX, launch_overlapped(route_gather_kernel<TX>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                             (const TX*)x, pair_at, pairs_per_row, (TX*)out, K, total));
+    return check_launch("route_gather");
+}
+
+// As gemm_grouped, for few rows per expert.  PH_ERR_UNSUPPORTED when K is not a multiple of 8 or a row is not
+// 16-byte aligned (the caller then takes gemm_grouped).
+PH_EXPORT int ph_gemv_grouped(const void* x, int x_dtype, const int32_t* pair_at, int pairs_per_row, const void* w, int w_dtype,
+                              const int32_t* tiles, int max_tiles, void* y, int y_dtype, int N, int K, cudaStream_t stream) {
+    if (!x || !w || !tiles || !y || max_tiles < 1 || N < 1 || K < 1 || pairs_per_row < 1 || !valid_dtype(x_dtype) ||
+        !valid_dtype(w_dtype) || !valid_dtype(y_dtype))
+        return fail(PH_ERR_ARG, "gemv_grouped: bad arguments (tiles %d, N %d, K %d)", max_tiles, N, K);
+    if (K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15))
+        return fail(PH_ERR_UNSUPPORTED, "gemv_grouped: K %d must be a multiple of 8 and the operands 16-byte aligned", K);
+    if (max_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "gemv_grouped: %d row tiles exceed the supported 65535", max_tiles);
+    dim3 grid((N + GV_WARPS - 1) / GV_WARPS, max_tiles);
+#define LAUNCH(TX, TW, TY)                                                                                                    \
+    launch_overlapped(gemv_grouped_kernel<TX, TW, TY>, grid, dim3(GV_WARPS * 32), 0, stream, (const TX*)x, pair_at, pairs_per_row, \
+                      (const TW*)w, tiles, (TY*)y, N, K)
+    PH_DISPATCH(x_dtype, TX, PH_DISPATCH(w_dtype, TW, PH_DISPATCH(y_dtype, TY, LAUNCH(TX, TW, TY))));
+#undef LAUNCH
+    return check_launch("gemv_grouped");
 }
 
 PH_EXPORT int ph_route_combine(const void* y, int y_dtype, const int32_t* position, const float* weight, int T, int top, int E_out,

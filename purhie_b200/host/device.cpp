@@ -165,6 +165,8 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_route_max_tiles", g_core.route_max_tiles);
     bind(h, "core", "ph_route_sort", g_core.route_sort);
     bind(h, "core", "ph_gemm_grouped", g_core.gemm_grouped);
+    bind(h, "core", "ph_gemv_grouped", g_core.gemv_grouped);
+    bind(h, "core", "ph_route_gather", g_core.route_gather);
     bind(h, "core", "ph_route_combine", g_core.route_combine);
     bind(h, "core", "ph_core_last_error", g_core.last_error);
     g_core_ok = true;

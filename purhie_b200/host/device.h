@@ -125,6 +125,9 @@ struct CoreKernels {
     int (*route_sort)(const int32_t*, int, int, int32_t*, int32_t*, int32_t*, int, int32_t*, cudaStream_t);
     int (*gemm_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
                         cudaStream_t);
+    int (*gemv_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
+                        cudaStream_t);
+    int (*route_gather)(const void*, int, const int32_t*, int, void*, int, int, cudaStream_t);
     int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, cudaStream_t);
     const char* (*last_error)(void);
 };

@@ -103,6 +103,32 @@ bool Linear::gives_partial_sums(int rows, bool allow_split) const {
     return plan_gemm(rows, (int)weight_.shape[0], (int)weight_.shape[1], sm_count(), allow_split, false).splits > 1;
 }
 
+void Linear::into(const Tensor& x_in, StepContext& ctx, Tensor out, int rows) const {
+    const int M = rows, N = (int)weight_.shape[0], K = (int)weight_.shape[1];
+    if (M == 0) return;
+    const CoreKernels& core = core_kernels();
+    Tensor x = x_in;
+    if (weight_.dtype == DType::F32 && x.dtype != DType::F32) {
+        Tensor x32 = ctx.workspace->get("linear_x32", {M, K}, DType::F32);
+        QE_LAUNCH(core, core.cast(x.data, x.code(), x32.data, x32.code(), (long long)M * K, ctx.stream));
+        x = x32;
+    }
+    if (LaunchProfile::get().on())
+        LaunchProfile::get().note_cost(2.0 * N * K + 2.0 * M * K + (double)M * N * dtype_size(out.dtype), 2.0 * M * N * K);
+    if (!(fast_ && x.dtype == DType::BF16)) {
+        QE_LAUNCH(core, core.gemm_simple(x.data, x.code(), weight_.data, weight_.code(), out.data, out.code(), M, N, K, ctx.stream));
+        return;
+    }
+    const GemmKernels& g = gemm_kernels();
+    const GemmPlan p = plan_gemm(M, N, K, sm_count(), false, false);
+    if (p.pair)
+        QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, 1, 0, 0, 0, nullptr, 0, 0, 0.0f, nullptr, nullptr,
+                                 nullptr, ctx.gemm_error, ctx.stream));
+    else
+        QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, 1, 0, 0, 0, nullptr, 0, 0, 0.0f,
+                            nullptr, nullptr, nullptr, ctx.gemm_error, ctx.stream));
+}
+
 Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
                           bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale, NormAhead* ahead) const {
     const int M = rows, N = (int)weight_.shape[0], K = (int)weight_.shape[1];

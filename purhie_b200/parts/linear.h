@@ -42,6 +42,9 @@ public:
     Addend operator()(const Tensor& x, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
                       bool allow_split = false, bool fuse_swiglu = false, float* add_into = nullptr,
                       const RowScale* scale = nullptr, NormAhead* ahead = nullptr) const;
+    // The plain product, K whole, written to `out` ([rows, out_features], any dtype the kernels write): for a caller
+    // that lays several products' results out side by side (the experts of a routed feed-forward).
+    void into(const Tensor& x, StepContext& ctx, Tensor out, int rows) const;
     // Few rows on the tensor-core kernel: the weight fills the wide side of the instruction (what plan_gemm calls
     // swapped).  Its partial sums are linear in the rows, and its bfloat16 epilogue can apply a factor per row.
     bool swapped_for(int rows, bool allow_split, bool fused_epilogue) const;

@@ -5,9 +5,15 @@
 // index on a tie) with weights softmax(z over the chosen).  An expert is the gated unit of feed_forward.cpp without
 // biases; the token's output is the weighted sum of its experts' outputs, added in the order of the choices.
 //
-// Everything stays on the device: the (token, choice) pairs are sorted by expert there, the experts' products run as
-// one launch per matrix over row tiles that never cross from one expert to the next, and no count reaches the host,
-// so a decode step with routing is captured as a graph like any other.
+// The (token, choice) pairs are sorted by expert on the device.  Which kernels then multiply:
+//   * few pairs (decoding): one launch per matrix of a kernel that streams each chosen expert's weight rows once
+//     (gemv_grouped); no count reaches the host, so the step is captured as a graph like any other;
+//   * a step with prompt portions in bfloat16: the counts per expert are read back (one small copy and a wait per
+//     layer; such steps are launched kernel by kernel anyway), the token rows are gathered in expert order, and every
+//     expert's rows go through the tensor-core product as one contiguous slice;
+//   * float32, or shapes the fast kernels refuse: gemm_grouped, the CUDA-core product over row tiles that never cross
+//     from one expert to the next, all on the device.
+// Whichever runs, a row's sum does not depend on what else is in the batch.
 #include <array>
 
 #include "gate.h"
@@ -67,6 +73,21 @@ public:
             src.release(up);
             src.release(down);
         }
+        // each expert's two matrices as products of their own, for the steps that run them slice by slice
+        const std::string gemm = compute_dtype == DType::BF16 ? "auto" : "simple";
+        for (int e = 0; e < experts_; e++) {
+            Tensor gu(static_cast<char*>(gate_up_.data) + (size_t)e * 2 * inter_ * hidden_ * dtype_size(gate_up_.dtype), gate_up_.dtype,
+                      {2 * inter_, hidden_});
+            Tensor dn(static_cast<char*>(down_.data) + (size_t)e * hidden_ * inter_ * dtype_size(down_.dtype), down_.dtype, {hidden_, inter_});
+            expert_gate_up_.emplace_back(gu, "expert_gate_up", gemm);
+            expert_down_.emplace_back(dn, "expert_down", gemm);
+        }
+        counts_host_.ensure((size_t)(experts_ + 1) * sizeof(int32_t));
+    }
+
+    std::vector<std::string> required_libraries() const override {
+        return (!expert_gate_up_.empty() && expert_gate_up_[0].fast()) ? std::vector<std::string>{"core", "gemm100"}
+                                                                         : std::vector<std::string>{"core"};
     }
 
     Addend forward(const Tensor& x, StepContext& ctx) override {
@@ -83,14 +104,46 @@ public:
         QE_LAUNCH(k, k.route_sort(choice.as<int32_t>(), R, experts_, position.as<int32_t>(), pair_at.as<int32_t>(),
                                   tile_list.as<int32_t>(), tiles, scratch.as<int32_t>(), ctx.stream));
         Tensor gu = ws.get("moe_gate_up", {R, 2 * inter_}, compute_dtype);
-        QE_LAUNCH(k, k.gemm_grouped(x.data, x.code(), pair_at.as<int32_t>(), top_, gate_up_.data, gate_up_.code(), tile_list.as<int32_t>(),
-                                    tiles, gu.data, gu.code(), (int)(2 * inter_), (int)hidden_, ctx.stream));
         Tensor act = ws.get("moe_act", {R, inter_}, compute_dtype);
+        Tensor y = ws.get("moe_down", {R, hidden_}, DType::F32);
+        const bool slices = !ctx.decode_only && R > kFewPairs && compute_dtype == DType::BF16 && x.dtype == DType::BF16 &&
+                            expert_gate_up_[0].fast() && expert_down_[0].fast() && hidden_ % 8 == 0 && inter_ % 8 == 0;
+        const bool few = !slices && R <= kFewPairs && hidden_ % 8 == 0 && inter_ % 8 == 0;
+        auto grouped = [&](const Tensor& in, const int32_t* pairs, int per_row, const Tensor& w, Tensor& out, int64_t N, int64_t K) {
+            if (few)
+                QE_LAUNCH(k, k.gemv_grouped(in.data, in.code(), pairs, per_row, w.data, w.code(), tile_list.as<int32_t>(), tiles, out.data,
+                                            out.code(), (int)N, (int)K, ctx.stream));
+            else
+                QE_LAUNCH(k, k.gemm_grouped(in.data, in.code(), pairs, per_row, w.data, w.code(), tile_list.as<int32_t>(), tiles, out.data,
+                                            out.code(), (int)N, (int)K, ctx.stream));
+        };
+        std::vector<int32_t> first(experts_ + 1, 0);
+        if (slices) {
+            // where each expert's rows start, on the host (the sort left them behind its counts), and x in that order
+            int32_t* host = static_cast<int32_t*>(counts_host_.data());
+            QE_CUDA(cudaMemcpyAsync(host, scratch.as<int32_t>() + experts_, (size_t)(experts_ + 1) * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                    ctx.stream));
+            Tensor xs = ws.get("moe_x_sorted", {R, hidden_}, x.dtype);
+            QE_LAUNCH(k, k.route_gather(x.data, x.code(), pair_at.as<int32_t>(), top_, xs.data, R, (int)hidden_, ctx.stream));
+            QE_CUDA(cudaStreamSynchronize(ctx.stream));
+            first.assign(host, host + experts_ + 1);
+            for (int e = 0; e < experts_; e++) {
+                const int at = first[e], n = first[e + 1] - first[e];
+                if (n > 0) expert_gate_up_[e].into(xs.rows(at, n), ctx, gu.rows(at, n), n);
+            }
+        } else {
+            grouped(x, pair_at.as<int32_t>(), top_, gate_up_, gu, 2 * inter_, hidden_);
+        }
         QE_LAUNCH(k, k.glu(gu.data, gu.code(), 1, 0, act.data, act.code(), R, (int)inter_, gate_.kind, gate_.alpha, gate_.limit,
                            gate_.shift, ctx.stream));
-        Tensor y = ws.get("moe_down", {R, hidden_}, DType::F32);
-        QE_LAUNCH(k, k.gemm_grouped(act.data, act.code(), nullptr, 1, down_.data, down_.code(), tile_list.as<int32_t>(), tiles, y.data,
-                                    y.code(), (int)hidden_, (int)inter_, ctx.stream));
+        if (slices) {
+            for (int e = 0; e < experts_; e++) {
+                const int at = first[e], n = first[e + 1] - first[e];
+                if (n > 0) expert_down_[e].into(act.rows(at, n), ctx, y.rows(at, n), n);
+            }
+        } else {
+            grouped(act, nullptr, 1, down_, y, hidden_, inter_);
+        }
         Tensor out = ws.get("moe_out", {T, hidden_}, DType::F32);
         QE_LAUNCH(k, k.route_combine(y.data, y.code(), position.as<int32_t>(), weight.as<float>(), T, top_, (int)hidden_, out.as<float>(),
                                      ctx.stream));
@@ -98,12 +151,15 @@ public:
     }
 
 private:
+    static constexpr int kFewPairs = 256;       // up to this many (token, choice) pairs a step streams the experts' rows
     int64_t hidden_, inter_;
     int experts_, top_;
     GateSpec gate_;
     bool has_bias_ = false;
     std::vector<std::array<std::string, 3>> expert_names_;
     Linear router_;
+    std::vector<Linear> expert_gate_up_, expert_down_;
+    PinnedBuffer counts_host_;
     Tensor router_bias_, gate_up_, down_;
 };
 

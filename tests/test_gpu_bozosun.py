@@ -126,6 +126,26 @@ def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, n
     eng.close()
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "bfloat16"), ("C", "float32")])
+def test_a_prompt_of_many_pairs_goes_through_the_tiled_expert_products(models, name, dtype):
+    """Past a few hundred (token, choice) pairs the experts' products change kernels: row tiles by expert on the CUDA
+    cores in float32, slices per expert through the tensor-core product in bfloat16."""
+    from purhie_b200.engine import StepEntry
+    folder, cfg, w = models[name]
+    eng = engine_for(folder, dtype, max_tokens=1024)
+    toks = tokens(330, cfg["vocab"], 11)
+    ref = P.forward(cfg, w, toks)
+    close(run_cut(eng, "whole", toks, []), ref, TOL[dtype])
+    # the same tokens as a long portion beside another request's decode row and a two-token portion
+    eng.add_request("a"); eng.add_request("b"); eng.add_request("c")
+    eng.step([StepEntry("b", toks[:5], []), StepEntry("c", toks[:9], [])])
+    out = eng.step([StepEntry("b", toks[5:6], [0]), StepEntry("a", toks[:300], list(range(300))), StepEntry("c", toks[9:11], [0, 1])])
+    close(out[1:301], ref[:300], TOL[dtype])
+    close(out[:1], ref[5:6], TOL[dtype])
+    close(out[301:], ref[9:11], TOL[dtype])
+    eng.close()
+
+
 def test_long_decoding_keeps_its_state(models):
     folder, cfg, w = models["A"]
     eng = engine_for(folder, "float32", max_tokens=256)
