@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
+    python bench.py --design bozosun [--size 2k|4k]      (another design beside the Qwen3 layers of equal size; see below)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on the
 device (CUDA events on the engine's stream) over exactly K decode steps after W warm-up steps, each step fed its
@@ -94,6 +95,93 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
+# ---- another design beside the closest existing one -------------------------------------------------------------------
+# Layer sizes that resemble a real model's, random weights.  Four layers, one of every pairing of the design's mixers
+# and feed-forwards; the twin is four Qwen3 layers of the same width, heads and feed-forward width.
+DESIGN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, inner=4096, state=16, dt_rank=128, conv=4, experts=8, top=2,
+               expert_ff=4096, vocab=32768),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, inner=8192, state=16, dt_rank=256, conv=4, experts=16, top=4,
+               expert_ff=3072, vocab=32768),
+}
+
+
+def bozosun_config(z):
+    rot = {"base": 1e6, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    att = lambda: {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                                  "rot": rot, "scale": z["dim"] ** -0.5, "v_mix": True}}
+    ssm = lambda: {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layers = [dict(att(), mlp=dense), dict(ssm(), mlp=moe), dict(att(), mlp=moe), dict(ssm(), mlp=dense)]
+    return {"architecture": "Bozosun", "vocab": z["vocab"], "width": z["width"], "residual_mult": 0.5, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": layers, "max_position": CONTEXT}
+
+
+def design_bench(args):
+    """Prefill and decode throughput of the design at real layer sizes beside its twin, and, kernel class by kernel
+    class, the time per call with the fraction of the roofline (bytes over the copy bandwidth or flops over the
+    cuBLAS rate, whichever is longer) from one profiled prompt and eight profiled decode steps."""
+    import numpy as np
+    from purhie_b200 import native
+    from purhie_b200.engine import Engine, StepEntry
+    z = DESIGN_SIZES[args.size]
+    pk = peaks()
+    twin = dict(QWEN3_8B, num_hidden_layers=4, hidden_size=z["width"], intermediate_size=z["ff"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=z["dim"], vocab_size=z["vocab"])
+    rng = np.random.default_rng(5)
+    batch, steps, warmup = args.batch, min(args.steps, 32), max(args.warmup, 3)
+    result = {"design": "bozosun", "size": args.size, "sizes": z, "batch": batch, "prefix": PREFIX, "prefill_tokens": PREFILL_TOKENS,
+              "peaks": pk, "models": {}}
+    for name, config in (("bozosun", bozosun_config(z)), ("qwen3_twin", twin)):
+        vocab = z["vocab"]
+        ids = lambda n: rng.integers(0, vocab, size=n).tolist()
+        eng = Engine.from_random(config, 3, "bfloat16", std=0.02, page_size=16, max_requests=batch + 2,
+                                 max_tokens=(batch + 1) * (PREFIX + 256) + PREFILL_TOKENS)
+        prompt = ids(PREFILL_TOKENS)
+
+        def prefill_once():
+            eng.add_request("p")
+            ms = eng.time_step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+            eng.release("p")
+            return ms
+        for _ in range(2):
+            prefill_once()
+        prefill_ms = sorted(prefill_once() for _ in range(5))[2]
+        for i in range(batch):
+            eng.add_request(i)
+            eng.step([StepEntry(i, ids(PREFIX), [])])
+        sampler = ClockSampler()
+        sampler.start()
+        ms_step, launches = eng.time_decode_steps(list(range(batch)), [ids(steps + warmup) for _ in range(batch)], warmup, steps, sample=True)
+        clocks = sampler.stop()
+        # one profiled prompt and eight profiled decode steps: every launcher between events, graphs off
+        native.lib().qe_profile_enable(1)
+        native.profile_report(True)
+        prefill_once()
+        prof_prefill = native.profile_report(True)
+        for _ in range(8):
+            eng.step([StepEntry(i, ids(1), [0]) for i in range(batch)])
+        prof_decode = native.profile_report(True)
+        native.lib().qe_profile_enable(0)
+
+        def classes(report):
+            out = {}
+            for k, v in sorted(report.items(), key=lambda kv: -kv[1]["ms"]):
+                us = 1e3 * v["ms"] / max(v["calls"], 1)
+                floor_us = max(v["bytes"] / v["calls"] / (pk["hbm_gbs"] * 1e3), v["flops"] / v["calls"] / (pk["bf16_tflops"] * 1e6)) if v["calls"] else 0.0
+                out[k] = {"calls": v["calls"], "us_per_call": round(us, 2), "roofline_us": round(floor_us, 2),
+                          "frac": round(floor_us / us, 3) if us > 0 and floor_us > 0 else None}
+            return out
+        result["models"][name] = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1),
+                                  "decode_ms_per_step": round(ms_step, 4), "decode_tok_s": round(batch / ms_step * 1e3, 1),
+                                  "decode_launches": launches, "clocks": clocks,
+                                  "prefill_kernels": classes(prof_prefill), "decode_kernels": classes(prof_decode)}
+        eng.close()
+    print(json.dumps(result))
+    return 0
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "the reference is a HIP engine for AMD gfx1151 (Makefile + hipcc, GGUF models); it has no Python "
@@ -117,6 +205,10 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the benchmark's configuration has 16)")
     ap.add_argument("--step-options", default="", metavar="JSON",
                     help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
+    ap.add_argument("--design", default="", choices=["", "bozosun"],
+                    help="instead of the headline workload: prefill and decode of this design at real layer sizes beside four "
+                         "Qwen3 layers of equal size, with the time and roofline fraction of every kernel class")
+    ap.add_argument("--size", default="4k", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
     ap.add_argument("--leave-out", default="", metavar="NAMES",
                     help="with --phase decode: launchers (comma separated, e.g. add_rmsnorm,decode_bulk) that the timed steps "
                          "skip; the difference to a run without shows what they cost inside the graph (no benchmark value)")
@@ -127,6 +219,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        return design_bench(args)
 
     import numpy as np
     from purhie_b200.api import GenOptions, load_model_random

@@ -32,6 +32,27 @@ __global__ void glu_kernel(const TI* __restrict__ gu, int splits, long long spli
     out[idx] = from_float<TO>(gated(gv, uv, kind, alpha, limit, shift));
 }
 
+// four outputs per thread: eight inputs in one or two 16-byte loads per split
+template <typename TI, typename TO>
+__global__ void glu_vec_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out, long long total4,
+                               int kind, float alpha, float limit, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= total4) return;
+    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s = 0; s < splits; ++s) {
+        float v[8];
+        load8(gu + (size_t)s * split_stride + q * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = gated(acc[2 * i], acc[2 * i + 1], kind, alpha, limit, shift);
+    store4(out + q * 4, o);
+}
+
 }  // namespace
 
 PH_EXPORT int ph_glu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out, int out_dtype, int T,
@@ -40,6 +61,13 @@ PH_EXPORT int ph_glu(const void* gate_up, int in_dtype, int splits, long long sp
         return fail(PH_ERR_ARG, "glu: bad arguments (T %d, FF %d, kind %d)", T, FF, kind);
     const long long total = (long long)T * FF;
     if (total == 0) return PH_OK;
+    if (FF % 4 == 0 && split_stride % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        const long long total4 = total / 4;
+        PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+            launch_overlapped(glu_vec_kernel<TI, TO>, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, stream, (const TI*)gate_up,
+                              splits, split_stride, (TO*)out, total4, kind, alpha, limit, shift)));
+        return check_launch("glu");
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
         launch_overlapped(glu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)gate_up, splits, split_stride,

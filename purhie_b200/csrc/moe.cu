@@ -1,8 +1,9 @@
 // Routing of a mixture of experts and the products of the chosen experts, all on the device (no count ever goes
 // to the host, so a step with routing can be captured as a graph).
 //
-//   route_topk     per token: the `top` largest of its float32 router logits (+ bias; the lower index wins a tie),
-//                  and the softmax over the chosen logits alone.
+//   route          per token: the router's logits w x + b in float32 (the router's matrix is float32 whatever the
+//                  model's dtype), the `top` largest of them (the lower index wins a tie), and the softmax over the
+//                  chosen logits alone.
 //   route_sort     the (token, choice) pairs sorted by expert: position of each pair, pair at each position, and a
 //                  list of row tiles (expert, first position, rows) that never cross from one expert to the next.
 //   gemm_grouped   y[i] = W[expert of i] x[source row of i] for the sorted positions i, tile by tile; float32
@@ -22,35 +23,88 @@ using namespace ph;
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 constexpr int MAX_TOP = 32;
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int top,
-                                  int32_t* __restrict__ choice, float* __restrict__ weight, int T) {
+// One block per token.  The warps share the experts: a warp's lanes walk k four elements at a time and add their parts
+// with a butterfly, so a logit's sum is taken in one order whatever the batch.  Then the first warp picks: `top` times
+// the largest logit not yet taken (the lower index on a tie), and the softmax over the picked ones.
+constexpr int RT_WARPS = 16, MAX_EXPERTS = 1024;
+
+// TOK tokens per block share every load of the router's rows (many tokens: the matrix is read TOK times less often).
+template <typename TX, int TOK>
+__global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
+                                                              const float* __restrict__ bias, int T, int E, int K, int top,
+                                                              int32_t* __restrict__ choice, float* __restrict__ weight) {
+    __shared__ float logit[TOK][MAX_EXPERTS / TOK];
+    __shared__ unsigned char taken[TOK][MAX_EXPERTS / TOK];
+    __shared__ float picked_value[TOK][MAX_TOP];
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= T) return;
-    const float* z = logits + (size_t)t * E;
-    int picked[MAX_TOP];
-    float value[MAX_TOP];
+    const int t0 = blockIdx.x * TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TX* xr[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) xr[i] = x + (size_t)(t0 + i < T ? t0 + i : t0) * K;
+    for (int e = warp; e < E; e += RT_WARPS) {
+        const float* wr = w + (size_t)e * K;
+        float acc[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) acc[i] = 0.0f;
+        if ((K & 3) == 0) {
+            for (int k0 = lane * 4; k0 < K; k0 += 512) {          // four strides of 128 elements in flight
+                float4 wv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    wv[u] = k0 + 128 * u < K ? *reinterpret_cast<const float4*>(wr + k0 + 128 * u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (k0 + 128 * u >= K) continue;
+                        const float4 xv = load4(xr[i] + k0 + 128 * u);
+                        acc[i] = fmaf(xv.x, wv[u].x, acc[i]);
+                        acc[i] = fmaf(xv.y, wv[u].y, acc[i]);
+                        acc[i] = fmaf(xv.z, wv[u].z, acc[i]);
+                        acc[i] = fmaf(xv.w, wv[u].w, acc[i]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32)
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) acc[i] = fmaf(to_float<TX>(xr[i][k]), wr[k], acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            const float total = warp_sum(acc[i]);
+            if (lane == 0) { logit[i][e] = total + (bias ? bias[e] : 0.0f); taken[i][e] = 0; }
+        }
+    }
+    __syncthreads();
+    if (warp >= TOK || t0 + warp >= T) return;                 // one warp per token picks
+    const int t = t0 + warp;
     for (int j = 0; j < top; ++j) {
         int best = -1;
         float best_v = 0.0f;
-        for (int e = 0; e < E; ++e) {
-            bool taken = false;
-            for (int i = 0; i < j; ++i) taken |= picked[i] == e;
-            if (taken) continue;
-            const float v = z[e] + (bias ? bias[e] : 0.0f);
-            if (best < 0 || v > best_v) { best = e; best_v = v; }
+        for (int e = lane; e < E; e += 32) {
+            if (taken[warp][e]) continue;
+            const float v = logit[warp][e];
+            if (best < 0 || v > best_v) { best = e; best_v = v; }      // ascending e: the lower index keeps a tie
         }
-        picked[j] = best;
-        value[j] = best_v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const int other = __shfl_xor_sync(0xffffffffu, best, o);
+            const float other_v = __shfl_xor_sync(0xffffffffu, best_v, o);
+            if (other >= 0 && (best < 0 || other_v > best_v || (other_v == best_v && other < best))) { best = other; best_v = other_v; }
+        }
+        if (lane == 0) {
+            taken[warp][best] = 1;
+            picked_value[warp][j] = best_v;
+            choice[(size_t)t * top + j] = best;
+        }
+        __syncwarp();
     }
-    const float largest = value[0];                       // the first pick
-    float sum = 0.0f;
-    for (int j = 0; j < top; ++j) { value[j] = expf(value[j] - largest); sum += value[j]; }
-    for (int j = 0; j < top; ++j) {
-        choice[(size_t)t * top + j] = picked[j];
-        weight[(size_t)t * top + j] = value[j] / sum;
-    }
+    const float largest = picked_value[warp][0];
+    const float mine = lane < top ? expf(picked_value[warp][lane] - largest) : 0.0f;
+    const float sum = warp_sum(mine);
+    if (lane < top) weight[(size_t)t * top + lane] = mine / sum;
 }
 
 // One block.  counts -> offsets -> a position for every pair; tiles[3 * i] = (expert, first position, rows), rows 0
@@ -155,18 +209,6 @@ __global__ void __launch_bounds__(256) gemm_grouped_kernel(const TX* __restrict_
     }
 }
 
-// eight consecutive elements as floats (16 bytes of bfloat16, 32 of float32)
-__device__ __forceinline__ void load8(const float* p, float* v) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(h[i]); v[2 * i + 1] = __high2float(h[i]); }
-}
-
 constexpr int GV_ROWS = 8, GV_WARPS = 8;
 
 // grid (ceil(N / GV_WARPS), tiles); K % 8 == 0 and 16-byte aligned rows (checked by the launcher)
@@ -224,6 +266,20 @@ __global__ void route_gather_kernel(const TX* __restrict__ x, const int32_t* __r
     const int k = (int)(idx % K);
     out[idx] = x[(size_t)(pair_at[i] / pairs_per_row) * K + k];
 }
+// the same, 16 bytes per thread (vec = elements of 16 bytes; K a multiple of it)
+template <typename TX>
+__global__ void route_gather_vec_kernel(const TX* __restrict__ x, const int32_t* __restrict__ pair_at, int pairs_per_row,
+                                        TX* __restrict__ out, int K, int vec, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int per_row = K / vec;
+    const long long i = idx / per_row;
+    const int k = (int)(idx % per_row) * vec;
+    *reinterpret_cast<uint4*>(out + (size_t)i * K + k) =
+        *reinterpret_cast<const uint4*>(x + (size_t)(pair_at[i] / pairs_per_row) * K + k);
+}
 
 template <typename TY>
 __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
@@ -239,16 +295,43 @@ __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __
     out[idx] = acc;
 }
 
+// float32 y, four columns per thread
+__global__ void route_combine_vec_kernel(const float* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
+                                         int top, float* __restrict__ out, int E_out, long long total4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int per_row = E_out / 4;
+    const int t = (int)(idx / per_row), c = (int)(idx % per_row) * 4;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int j = 0; j < top; ++j) {
+        const float wj = weight[(size_t)t * top + j];
+        const float4 v = *reinterpret_cast<const float4*>(y + (size_t)position[(size_t)t * top + j] * E_out + c);
+        acc.x += wj * v.x; acc.y += wj * v.y; acc.z += wj * v.z; acc.w += wj * v.w;
+    }
+    *reinterpret_cast<float4*>(out + (size_t)t * E_out + c) = acc;
+}
+
 }  // namespace
 
-PH_EXPORT int ph_route_topk(const float* logits, const float* bias, int T, int E, int top, int32_t* choice, float* weight,
-                            cudaStream_t stream) {
-    if (!logits || !choice || !weight || T < 0 || E < 1 || top < 1 || top > E)
-        return fail(PH_ERR_ARG, "route_topk: bad arguments (T %d, experts %d, top %d)", T, E, top);
-    if (top > MAX_TOP) return fail(PH_ERR_UNSUPPORTED, "route_topk: top %d exceeds the supported %d", top, MAX_TOP);
+// x [T, K] (the model's dtype), w [E, K] float32, bias [E] or null -> choice [T, top], weight [T, top].
+PH_EXPORT int ph_route(const void* x, int x_dtype, const float* w, const float* bias, int T, int E, int K, int top, int32_t* choice,
+                       float* weight, cudaStream_t stream) {
+    if (!x || !w || !choice || !weight || T < 0 || E < 1 || K < 1 || top < 1 || top > E || !valid_dtype(x_dtype))
+        return fail(PH_ERR_ARG, "route: bad arguments (T %d, experts %d, K %d, top %d)", T, E, K, top);
+    if (top > MAX_TOP || E > MAX_EXPERTS)
+        return fail(PH_ERR_UNSUPPORTED, "route: top %d of %d experts exceeds the supported %d of %d", top, E, MAX_TOP, MAX_EXPERTS);
     if (T == 0) return PH_OK;
-    launch_overlapped(route_topk_kernel, dim3((T + 63) / 64), dim3(64), 0, stream, logits, bias, E, top, choice, weight, T);
-    return check_launch("route_topk");
+    const bool aligned = (((uintptr_t)x | (uintptr_t)w) & 15) == 0 || (K & 3) != 0;
+    if (!aligned) return fail(PH_ERR_ARG, "route: the rows must be 16-byte aligned");
+    if (T >= 64 && E <= MAX_EXPERTS / 4)
+        PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 4>, dim3((T + 3) / 4), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w,
+                                                   bias, T, E, K, top, choice, weight));
+    else
+        PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 1>, dim3(T), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w, bias, T,
+                                                   E, K, top, choice, weight));
+    return check_launch("route");
 }
 
 PH_EXPORT int ph_route_max_tiles(int R, int E) { return (R + BM - 1) / BM + E; }
@@ -287,6 +370,13 @@ PH_EXPORT int ph_route_gather(const void* x, int dtype, const int32_t* pair_at, 
         return fail(PH_ERR_ARG, "route_gather: bad arguments (rows %d, K %d)", R, K);
     const long long total = (long long)R * K;
     if (total == 0) return PH_OK;
+    const int vec = dtype == PH_F32 ? 4 : 8;
+    if (K % vec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const long long n = total / vec;
+        PH_DISPATCH(dtype, TX, launch_overlapped(route_gather_vec_kernel<TX>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                                                 (const TX*)x, pair_at, pairs_per_row, (TX*)out, K, vec, n));
+        return check_launch("route_gather");
+    }
     PH_DISPATCH(dtype, TX, launch_overlapped(route_gather_kernel<TX>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
                                              (const TX*)x, pair_at, pairs_per_row, (TX*)out, K, total));
     return check_launch("route_gather");
@@ -317,6 +407,11 @@ PH_EXPORT int ph_route_combine(const void* y, int y_dtype, const int32_t* positi
         return fail(PH_ERR_ARG, "route_combine: bad arguments (T %d, top %d, width %d)", T, top, E_out);
     const long long total = (long long)T * E_out;
     if (total == 0) return PH_OK;
+    if (y_dtype == PH_F32 && E_out % 4 == 0 && (((uintptr_t)y | (uintptr_t)out) & 15) == 0) {
+        launch_overlapped(route_combine_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (const float*)y, position,
+                          weight, top, out, E_out, total / 4);
+        return check_launch("route_combine");
+    }
     PH_DISPATCH(y_dtype, TY, launch_overlapped(route_combine_kernel<TY>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
                                                (const TY*)y, position, weight, top, out, E_out, total));
     return check_launch("route_combine");

@@ -161,7 +161,7 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_glu", g_core.glu);
     bind(h, "core", "ph_causal_conv_silu", g_core.causal_conv_silu);
     bind(h, "core", "ph_selective_scan", g_core.selective_scan);
-    bind(h, "core", "ph_route_topk", g_core.route_topk);
+    bind(h, "core", "ph_route", g_core.route);
     bind(h, "core", "ph_route_max_tiles", g_core.route_max_tiles);
     bind(h, "core", "ph_route_sort", g_core.route_sort);
     bind(h, "core", "ph_gemm_grouped", g_core.gemm_grouped);

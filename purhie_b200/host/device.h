@@ -118,9 +118,9 @@ struct CoreKernels {
                             const int32_t*, const int32_t*, const int32_t*, void*, int, int, cudaStream_t);
     int (*selective_scan)(const void*, const float*, const float*, const void*, long long, int, int, int, const float*,
                           const float*, const void*, long long, int, int, float*, long long, const int32_t*, const int32_t*, int,
-                          void*, int, cudaStream_t);
-    // routing: top-k with softmax over the chosen, sort by expert, products by expert, weighted sum
-    int (*route_topk)(const float*, const float*, int, int, int, int32_t*, float*, cudaStream_t);
+                          const int32_t*, int, const int32_t*, float*, float*, void*, int, cudaStream_t);
+    // routing: router logits and top-k with softmax over the chosen, sort by expert, products by expert, weighted sum
+    int (*route)(const void*, int, const float*, const float*, int, int, int, int, int32_t*, float*, cudaStream_t);
     int (*route_max_tiles)(int, int);
     int (*route_sort)(const int32_t*, int, int, int32_t*, int32_t*, int32_t*, int, int32_t*, cudaStream_t);
     int (*gemm_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,

@@ -277,6 +277,10 @@ public:
         Tensor q = ws.get("q", {T, heads_, head_dim_}, dt);
         const int column = position_ ? position_->position_column() : 0;
         const int32_t* positions = ctx.position_column(column);
+        if (LaunchProfile::get().on()) {       // reads the product's rows (every split), writes q and the cache rows
+            const double row = (double)(q_width_ + (int64_t)kv_heads_written * (head_dim_ + value_dim_));
+            LaunchProfile::get().note_cost((double)T * row * (qkv.splits * dtype_size(qkv.tensor.dtype) + dtype_size(dt)), 0.0);
+        }
         QE_LAUNCH(core, core.qk_norm_rope_kv_write(
             qkv.tensor.data, qkv.tensor.code(), qkv.splits, (long long)T * (q_width_ + (int64_t)kv_heads_written * (head_dim_ + value_dim_)),
             bias_.defined() ? bias_.as<float>() : nullptr, has_norm_ ? q_norm_.as<float>() : nullptr,
@@ -288,6 +292,20 @@ public:
             mix_factor_.defined() ? mix_factor_.as<float>() : nullptr, value_mix_, ctx.stream));
         Tensor out = ws.get("attn_out", {T, o_width_}, dt);
         const int32_t* abs_positions = ctx.position_column(0);       // the mask always follows the index in the request
+        if (LaunchProfile::get().on()) {
+            // keys and values each row looks back over (read once per request and kv head at best), q in, the output out;
+            // two products of a row with every key it sees
+            double seen = 0.0, read = 0.0;
+            for (size_t i = 0; i < ctx.q_lens.size(); i++) {
+                const double n = ctx.q_lens[i], len = ctx.ctx_lens[i];
+                const double span = window_ ? std::min<double>(len, window_ + n) : len;
+                read += span;
+                seen += window_ ? n * std::min<double>(len, window_) : n * (len - n) + n * (n + 1) / 2.0;
+            }
+            const double kv = dtype_size(cache.kv_dtype);
+            LaunchProfile::get().note_cost(read * kv_heads_ * (head_dim_ + value_dim_) * kv + (double)T * (q_width_ + o_width_) * dtype_size(dt),
+                                           2.0 * seen * heads_ * (head_dim_ + value_dim_));
+        }
         if (use_flash()) {
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
             flash(q, cache, g, ctx, out, abs_positions);

@@ -58,6 +58,8 @@ public:
         else {
             act = ctx.workspace->get("ff_act", {T, inter_}, compute_dtype);
             const CoreKernels& k = core_kernels();
+            if (LaunchProfile::get().on())
+                LaunchProfile::get().note_cost((double)T * inter_ * (2.0 * gu.splits * dtype_size(gu.tensor.dtype) + dtype_size(compute_dtype)), 0.0);
             if (gate_.kind == 0)
                 QE_LAUNCH(k, k.swiglu(gu.tensor.data, gu.tensor.code(), gu.splits, (long long)T * 2 * inter_, act.data, act.code(), T,
                                       (int)inter_, ctx.stream));

@@ -14,6 +14,7 @@
 // The step projection is run as one product over the whole [dt_low | B | C] row with zero columns under B and C
 // (the weight is widened once, when the model is bound), so that no strided copy of dt_low is needed; a zero times a
 // finite number adds nothing, so the sums are the ones of the narrow product.
+#include <algorithm>
 #include <cmath>
 
 #include "linear.h"
@@ -84,6 +85,28 @@ public:
 
     CacheNeed cache_need() const override { return CacheNeed::state({state_floats()}, DType::F32); }
 
+    // A step with a long prompt portion cuts every request's rows into chunks for the scan (first row, rows, segment,
+    // 1 if the request's last chunk), so that a prompt's tokens are spread over the device: the chunk list is this
+    // mixer's own metadata, shared by all layers of its kind.
+    void prepare_step(StepPlan& plan) override {
+        if (plan.has("ssm.chunks")) return;
+        int longest = 0;
+        for (int n : plan.q_lens) longest = std::max(longest, n);
+        if (longest < kChunkFrom) return;
+        std::vector<int32_t> items, seg_items = {0};
+        int row = 0;
+        for (int s = 0; s < plan.S; s++) {
+            const int n = plan.q_lens[s];
+            for (int at = 0; at < n; at += kChunk) {
+                items.push_back(row + at); items.push_back(std::min(kChunk, n - at)); items.push_back(s); items.push_back(at + kChunk >= n);
+            }
+            row += n;
+            seg_items.push_back((int32_t)(items.size() / 4));
+        }
+        plan.add("ssm.chunks", std::move(items));
+        plan.add("ssm.seg_chunks", std::move(seg_items));
+    }
+
     Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
         if (cache.kind != CacheNeed::State || !cache.state.defined() || cache.state.dtype != DType::F32 ||
             cache.state.shape.size() != 2 || cache.state.shape[1] != state_floats())
@@ -95,19 +118,35 @@ public:
         Tensor uz = in_proj_(x, ctx, "ssm_uz", dt, T).tensor;                                   // [T, 2 inner]
         Tensor xc = ws.get("ssm_x", {T, inner_}, dt);
         const long long conv_at = (long long)inner_ * state_;
+        const double es = (double)dtype_size(dt);
+        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost((double)T * inner_ * 2.0 * es, 2.0 * T * inner_ * taps_);
         QE_LAUNCH(k, k.causal_conv_silu(uz.data, uz.code(), 2 * inner_, (int)inner_, conv_w_.as<float>(), conv_b_.as<float>(), taps_,
                                         cache.state.as<float>(), state_floats(), conv_at, ctx.row_seg, ctx.seg_start, ctx.seg_slot,
                                         xc.data, xc.code(), T, ctx.stream));
         Tensor low = x_proj_(xc, ctx, "ssm_low", dt, T).tensor;                                 // [T, rank + 2 state]
         Tensor dt_raw = dt_proj_(low, ctx, "ssm_dt", DType::F32, T).tensor;                     // [T, inner]
         Tensor y = ws.get("ssm_y", {T, inner_}, dt);
+        const StepArray chunks = ctx.array("ssm.chunks"), seg_chunks = ctx.array("ssm.seg_chunks");
+        const int n_chunks = chunks.count / 4;
+        float *carry = nullptr, *dt_sum = nullptr;
+        if (n_chunks) {
+            carry = ws.get("ssm_carry", {n_chunks, inner_, state_}, DType::F32).as<float>();
+            dt_sum = ws.get("ssm_dt_sum", {n_chunks, inner_}, DType::F32).as<float>();
+        }
+        if (LaunchProfile::get().on())          // x, z, dt and y per token and channel, B and C per token, the state in and out
+            LaunchProfile::get().note_cost((double)T * inner_ * (3.0 * es + 4.0) + (double)T * 2.0 * state_ * es +
+                                               2.0 * ctx.S * (double)state_floats() * 4.0,
+                                           (double)T * inner_ * state_ * 6.0);
         QE_LAUNCH(k, k.selective_scan(xc.data, dt_raw.as<float>(), dt_bias_.as<float>(), low.data, low_width_, rank_, rank_ + state_, state_,
                                       a_.as<float>(), d_.as<float>(), uz.data, 2 * inner_, (int)inner_, taps_, cache.state.as<float>(),
-                                      state_floats(), ctx.seg_start, ctx.seg_slot, ctx.S, y.data, y.code(), ctx.stream));
+                                      state_floats(), ctx.seg_start, ctx.seg_slot, ctx.S, n_chunks ? chunks.data : nullptr, n_chunks,
+                                      n_chunks ? seg_chunks.data : nullptr, carry, dt_sum, y.data, y.code(), ctx.stream));
         return out_proj_(y, ctx, "ssm_out", DType::F32, T, true);
     }
 
 private:
+    static constexpr int kChunk = 64;           // tokens of a chunk of the scan
+    static constexpr int kChunkFrom = 192;      // the longest portion of a step from which its scan runs in chunks
     int64_t state_floats() const { return inner_ * state_ + (int64_t)(taps_ - 1) * inner_; }
     int64_t hidden_, inner_, low_width_;
     int state_, rank_, taps_;

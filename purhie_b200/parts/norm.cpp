@@ -11,6 +11,14 @@ AddendTransform Norm::as_transform(float) const {
 }
 
 namespace {
+// what a norm's pass over the rows moves: the residual read (and written back when an addend is folded in), the
+// addend's parts, the normed rows
+void note_norm_cost(const ResidualStream& stream, int rows, int64_t width, DType out, bool write_back) {
+    if (!LaunchProfile::get().on()) return;
+    double bytes = 4.0 * rows * width + (double)rows * width * dtype_size(out);
+    if (stream.has_pending) bytes += (double)stream.pending.splits * rows * width * dtype_size(stream.pending.tensor.dtype) + (write_back ? 4.0 * rows * width : 0.0);
+    LaunchProfile::get().note_cost(bytes, 0.0);
+}
 // x += factor * norm(addend) for a pending addend with a transform, by the kernel that knows transforms; afterwards
 // the stream has nothing pending.  For norms whose own kernel does not know them.
 void fold_transformed(ResidualStream& stream, StepContext& ctx) {
@@ -40,6 +48,7 @@ public:
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
+        note_norm_cost(stream, n, size_, compute_dtype, !rows);
         QE_LAUNCH(k, k.add_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
                                    pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
                                    (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1, ctx.stream));
@@ -66,6 +75,7 @@ public:
         Tensor sumsq = ctx.workspace->get("normed_sumsq", {ctx.T, chunks}, DType::F32);
         const CoreKernels& k = core_kernels();
         const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
+        note_norm_cost(stream, ctx.T, size_, compute_dtype, true);
         QE_LAUNCH(k, k.add_weight_sumsq(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
                                         pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(), ctx.T,
                                         (int)size_, out.data, out.code(), sumsq.as<float>(), chunks, ctx.stream));
@@ -109,6 +119,7 @@ public:
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* a = stream.has_pending ? &stream.pending : nullptr;
+        note_norm_cost(stream, n, size_, compute_dtype, !rows);
         QE_LAUNCH(k, k.add_layernorm(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
                                      a ? (long long)ctx.T * size_ : 0, a ? a->transform.weight : nullptr, a ? a->transform.bias : nullptr,
                                      a ? a->transform.eps : 0.0f, a ? a->transform.factor : 1.0f, weight_.as<float>(),

@@ -14,6 +14,7 @@
 //   * float32, or shapes the fast kernels refuse: gemm_grouped, the CUDA-core product over row tiles that never cross
 //     from one expert to the next, all on the device.
 // Whichever runs, a row's sum does not depend on what else is in the batch.
+#include <algorithm>
 #include <array>
 
 #include "gate.h"
@@ -50,7 +51,7 @@ public:
     }
 
     void bind(WeightSource& src) override {
-        router_ = Linear(src.fetch(name_of("router")), "router", "simple");
+        router_ = src.fetch(name_of("router"));
         if (has_bias_) router_bias_ = src.fetch(name_of("router_bias"));
         // the experts' matrices stacked: [experts, 2 ff, hidden] with gate and up rows interleaved (g0, u0, g1, u1, ...)
         // as the gated feed-forward lays them out, and [experts, hidden, ff]
@@ -94,10 +95,11 @@ public:
         const int T = ctx.T, R = T * top_;
         Workspace& ws = *ctx.workspace;
         const CoreKernels& k = core_kernels();
-        Tensor logits = router_(x, ctx, "moe_router", DType::F32, T).tensor;
         Tensor choice = ws.get("moe_choice", {T, top_}, DType::I32), weight = ws.get("moe_weight", {T, top_}, DType::F32);
-        QE_LAUNCH(k, k.route_topk(logits.as<float>(), router_bias_.defined() ? router_bias_.as<float>() : nullptr, T, experts_, top_,
-                                  choice.as<int32_t>(), weight.as<float>(), ctx.stream));
+        if (LaunchProfile::get().on())
+            LaunchProfile::get().note_cost((double)T * hidden_ * dtype_size(x.dtype) + 4.0 * experts_ * hidden_, 2.0 * T * experts_ * hidden_);
+        QE_LAUNCH(k, k.route(x.data, x.code(), router_.as<float>(), router_bias_.defined() ? router_bias_.as<float>() : nullptr, T, experts_,
+                             (int)hidden_, top_, choice.as<int32_t>(), weight.as<float>(), ctx.stream));
         const int tiles = k.route_max_tiles(R, experts_);
         Tensor position = ws.get("moe_position", {R}, DType::I32), pair_at = ws.get("moe_pair_at", {R}, DType::I32);
         Tensor tile_list = ws.get("moe_tiles", {tiles, 3}, DType::I32), scratch = ws.get("moe_sort_scratch", {3 * experts_ + 1}, DType::I32);
@@ -110,6 +112,11 @@ public:
                             expert_gate_up_[0].fast() && expert_down_[0].fast() && hidden_ % 8 == 0 && inter_ % 8 == 0;
         const bool few = !slices && R <= kFewPairs && hidden_ % 8 == 0 && inter_ % 8 == 0;
         auto grouped = [&](const Tensor& in, const int32_t* pairs, int per_row, const Tensor& w, Tensor& out, int64_t N, int64_t K) {
+            if (LaunchProfile::get().on()) {     // the matrices of the experts that can have been chosen, the rows in and out
+                const double touched = std::min<double>(experts_, R);
+                LaunchProfile::get().note_cost(touched * N * K * dtype_size(w.dtype) + (double)R * (K * dtype_size(in.dtype) + N * dtype_size(out.dtype)),
+                                               2.0 * R * N * K);
+            }
             if (few)
                 QE_LAUNCH(k, k.gemv_grouped(in.data, in.code(), pairs, per_row, w.data, w.code(), tile_list.as<int32_t>(), tiles, out.data,
                                             out.code(), (int)N, (int)K, ctx.stream));
@@ -134,6 +141,7 @@ public:
         } else {
             grouped(x, pair_at.as<int32_t>(), top_, gate_up_, gu, 2 * inter_, hidden_);
         }
+        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost(3.0 * R * inter_ * dtype_size(compute_dtype), 0.0);
         QE_LAUNCH(k, k.glu(gu.data, gu.code(), 1, 0, act.data, act.code(), R, (int)inter_, gate_.kind, gate_.alpha, gate_.limit,
                            gate_.shift, ctx.stream));
         if (slices) {
@@ -157,10 +165,9 @@ private:
     GateSpec gate_;
     bool has_bias_ = false;
     std::vector<std::array<std::string, 3>> expert_names_;
-    Linear router_;
     std::vector<Linear> expert_gate_up_, expert_down_;
     PinnedBuffer counts_host_;
-    Tensor router_bias_, gate_up_, down_;
+    Tensor router_, router_bias_, gate_up_, down_;
 };
 
 void register_routed_parts() {

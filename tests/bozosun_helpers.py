@@ -125,6 +125,24 @@ def draw_weights(cfg, seed, std=0.3):
     return out
 
 
+def steady_routing(cfg, weights, seed=0):
+    """The same weights with router biases that decide which experts are chosen, a different set in every layer: the
+    chosen `top` lie 60 above the rest and within 1 of each other, so that their weights still follow the token while a
+    rounding of the router's input cannot change the set (what a reduced-precision run needs to be comparable at all)."""
+    rng = np.random.default_rng(seed)
+    out = dict(weights)
+    for i, layer in enumerate(cfg["layers"]):
+        mlp = layer.get("mlp")
+        if not mlp or mlp["kind"] != "moe":
+            continue
+        experts, top = mlp["router"]["experts"], mlp["router"]["top"]
+        bias = np.full(experts, -30.0, dtype=np.float32)
+        chosen = rng.permutation(experts)[:top]
+        bias[chosen] = 30.0 + rng.uniform(0.0, 1.0, top).astype(np.float32)
+        out[f"l{i}.mlp.router.b"] = bf16_round(bias)
+    return out
+
+
 def make_folder(folder, cfg, weights, dtype="F32"):
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:

@@ -10,7 +10,7 @@ import pytest
 
 from plain import bozosun_plain as P
 from bozosun_helpers import (CONFIG_A, CONFIG_B, CONFIG_C, YARN, attention, bf16_round, config, dense, draw_weights, make_folder,
-                             mamba, moe, rot, tokens)
+                             mamba, moe, rot, steady_routing, tokens)
 
 pytestmark = pytest.mark.gpu
 
@@ -22,14 +22,26 @@ def f64(w):
     return {k: np.asarray(v, dtype=np.float64) for k, v in w.items()}
 
 
+class Models:
+    """Per configuration and dtype: (folder, config, weights for the plain implementation).  The float32 runs read
+    weights stored in 32 bits with routers left free; the bfloat16 runs read the same values stored as bfloat16 (which
+    is what puts the tensor-core products to work) with routers whose choice a rounding cannot change."""
+
+    def __init__(self, factory):
+        self.items = {}
+        for i, (name, cfg) in enumerate(CONFIGS.items()):
+            w = draw_weights(cfg, 100 + i)
+            self.items[name, "float32"] = (make_folder(factory.mktemp(f"bz_{name}_f32"), cfg, w, "F32"), cfg, f64(w))
+            ws = steady_routing(cfg, w, i)
+            self.items[name, "bfloat16"] = (make_folder(factory.mktemp(f"bz_{name}_bf16"), cfg, ws, "BF16"), cfg, f64(ws))
+
+    def __getitem__(self, key):
+        return self.items[key if isinstance(key, tuple) else (key, "float32")]
+
+
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
-    out = {}
-    for i, (name, cfg) in enumerate(CONFIGS.items()):
-        w = draw_weights(cfg, 100 + i)
-        folder = make_folder(tmp_path_factory.mktemp(f"bz_{name}"), cfg, w)
-        out[name] = (folder, cfg, f64(w))
-    return out
+    return Models(tmp_path_factory)
 
 
 def engine_for(folder, dtype, **kw):
@@ -66,7 +78,7 @@ def run_cut(engine, rid, toks, cuts):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_whole_prompts_cuts_and_decoding_agree_with_the_plain_implementation(models, name, dtype):
-    folder, cfg, w = models[name]
+    folder, cfg, w = models[name, dtype]
     eng = engine_for(folder, dtype)
     toks = tokens(75, cfg["vocab"], 7)
     ref = P.forward(cfg, w, toks)
@@ -89,7 +101,7 @@ def test_whole_prompts_cuts_and_decoding_agree_with_the_plain_implementation(mod
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(models, name, dtype):
     from purhie_b200.engine import StepEntry
-    folder, cfg, w = models[name]
+    folder, cfg, w = models[name, dtype]
     # room for two requests' states and about 100 tokens: five requests must take turns, pages come back poisoned
     eng = engine_for(folder, dtype, max_tokens=104, max_requests=2)
     lengths = [41, 9, 1, 56, 23]
@@ -131,7 +143,7 @@ def test_a_prompt_of_many_pairs_goes_through_the_tiled_expert_products(models, n
     """Past a few hundred (token, choice) pairs the experts' products change kernels: row tiles by expert on the CUDA
     cores in float32, slices per expert through the tensor-core product in bfloat16."""
     from purhie_b200.engine import StepEntry
-    folder, cfg, w = models[name]
+    folder, cfg, w = models[name, dtype]
     eng = engine_for(folder, dtype, max_tokens=1024)
     toks = tokens(330, cfg["vocab"], 11)
     ref = P.forward(cfg, w, toks)
