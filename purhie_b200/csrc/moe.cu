@@ -209,9 +209,11 @@ __global__ void __launch_bounds__(256) gemm_grouped_kernel(const TX* __restrict_
     }
 }
 
-constexpr int GV_ROWS = 8, GV_WARPS = 8;
+constexpr int GV_ROWS = 8, GV_WARPS = 8, GV_FEATURES = 4;
 
-// grid (ceil(N / GV_WARPS), tiles); K % 8 == 0 and 16-byte aligned rows (checked by the launcher)
+// grid (ceil(N / (GV_WARPS * GV_FEATURES)), tiles); K % 8 == 0 and 16-byte aligned rows (checked by the launcher).  A warp
+// streams GV_FEATURES weight rows side by side (as many 16-byte loads in flight per lane, and every load of x used that
+// many times); the sum of one (row, feature) is taken lane by lane over k ascending, then by a butterfly.
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_grouped_kernel(const TX* __restrict__ x, const int32_t* __restrict__ pair_at,
                                                                      int pairs_per_row, const TW* __restrict__ w,
@@ -221,35 +223,46 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_grouped_kernel(const TX* _
     const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
     if (rows == 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * GV_WARPS + warp;
-    if (n >= N) return;
-    const TW* wr = w + ((size_t)expert * N + n) * K;
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_FEATURES;
+    if (n0 >= N) return;
+    const TW* wr[GV_FEATURES];
+#pragma unroll
+    for (int f = 0; f < GV_FEATURES; ++f) wr[f] = w + ((size_t)expert * N + (n0 + f < N ? n0 + f : n0)) * K;
     for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
         const TX* xr[GV_ROWS];
 #pragma unroll
         for (int r = 0; r < GV_ROWS; ++r) {
-            const int i = row0 + r0 + (r0 + r < rows ? r : 0);             // rows past the end repeat the first (never stored)
+            const int i = row0 + r0 + (r0 + r < rows ? r : 0);             // rows past the end repeat the first (never used)
             xr[r] = x + (size_t)(pair_at ? pair_at[i] / pairs_per_row : i) * K;
         }
-        float acc[GV_ROWS];
+        float acc[GV_ROWS][GV_FEATURES];
 #pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) acc[r] = 0.0f;
+        for (int r = 0; r < GV_ROWS; ++r)
+#pragma unroll
+            for (int f = 0; f < GV_FEATURES; ++f) acc[r][f] = 0.0f;
         for (int k = lane * 8; k < K; k += 32 * 8) {
-            float wv[8];
-            load8(wr + k, wv);
+            float wv[GV_FEATURES][8];
+#pragma unroll
+            for (int f = 0; f < GV_FEATURES; ++f) load8(wr[f] + k, wv[f]);
 #pragma unroll
             for (int r = 0; r < GV_ROWS; ++r) {
                 if (r0 + r >= rows) continue;                              // the same for the whole block
                 float xv[8];
                 load8(xr[r] + k, xv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[r] = fmaf(xv[j], wv[j], acc[r]);
+                for (int f = 0; f < GV_FEATURES; ++f)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[r][f] = fmaf(xv[j], wv[f][j], acc[r][f]);
             }
         }
 #pragma unroll
         for (int r = 0; r < GV_ROWS; ++r) {
-            const float total = warp_sum(acc[r]);
-            if (lane == 0 && r0 + r < rows) y[(size_t)(row0 + r0 + r) * N + n] = from_float<TY>(total);
+            if (r0 + r >= rows) continue;
+#pragma unroll
+            for (int f = 0; f < GV_FEATURES; ++f) {
+                const float total = warp_sum(acc[r][f]);
+                if (lane == 0 && n0 + f < N) y[(size_t)(row0 + r0 + r) * N + n0 + f] = from_float<TY>(total);
+            }
         }
     }
 }
@@ -392,7 +405,7 @@ PH_EXPORT int ph_gemv_grouped(const void* x, int x_dtype, const int32_t* pair_at
     if (K % 8 || (((uintptr_t)x | (uintptr_t)w) & 15))
         return fail(PH_ERR_UNSUPPORTED, "gemv_grouped: K %d must be a multiple of 8 and the operands 16-byte aligned", K);
     if (max_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "gemv_grouped: %d row tiles exceed the supported 65535", max_tiles);
-    dim3 grid((N + GV_WARPS - 1) / GV_WARPS, max_tiles);
+    dim3 grid((N + GV_WARPS * GV_FEATURES - 1) / (GV_WARPS * GV_FEATURES), max_tiles);
 #define LAUNCH(TX, TW, TY)                                                                                                    \
     launch_overlapped(gemv_grouped_kernel<TX, TW, TY>, grid, dim3(GV_WARPS * 32), 0, stream, (const TX*)x, pair_at, pairs_per_row, \
                       (const TW*)w, tiles, (TY*)y, N, K)

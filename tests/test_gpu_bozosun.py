@@ -188,6 +188,22 @@ def test_greedy_generation_through_the_entry_point_and_the_scheduler(models):
     model.free()
 
 
+def test_the_command_line_generates_from_a_folder_of_this_design(models):
+    import subprocess
+    import sys
+    from helpers import ROOT
+    folder, cfg, w = models["A"]
+    prompt = tokens(12, cfg["vocab"], 8)
+    toks = list(prompt)
+    for _ in range(5):
+        toks.append(int(P.forward(cfg, w, toks)[-1].argmax()))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen_demo"), folder, ",".join(map(str, prompt)), "5", "--dtype", "float32",
+                        "--ctx", "64"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.strip().splitlines()
+    assert [int(x) for x in lines[2:7]] == toks[12:]
+
+
 def test_trace_replay_reads_a_folder_of_this_design(models, tmp_path):
     from helpers import TraceRun
     folder, cfg, w = models["B"]
