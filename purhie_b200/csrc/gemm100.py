@@ -18,9 +18,9 @@ from .ops import KernelError, call, register_signatures
 
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p],
-    "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                   c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
 })
 
@@ -30,6 +30,16 @@ _sm_count = {}
 
 ERRORS = {101: "the TMA producer waited too long for a free stage", 102: "the MMA warp waited too long",
           103: "the epilogue waited too long for an accumulator"}
+
+
+def _gate_pointer(gate):
+    """``gate``: None (the silu gate) or (alpha, limit, shift) of the clamped swish, as three floats on the host."""
+    if gate is None:
+        return None
+    import ctypes
+    arr = (ctypes.c_float * 3)(*[float(v) for v in gate])
+    _gate_pointer.keep = arr                       # alive until the call has read it
+    return ctypes.addressof(arr)
 
 
 def supports(weight: torch.Tensor) -> bool:
@@ -65,7 +75,7 @@ def sm_count(device) -> int:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, block_n: int, splits: int = 1,
-         max_ctas: int = 0, swiglu: bool = False, accumulate: bool = False, row_sumsq: Optional[torch.Tensor] = None,
+         max_ctas: int = 0, swiglu: bool = False, accumulate: bool = False, row_sumsq: Optional[torch.Tensor] = None, gate=None,
          row_width: int = 0, row_eps: float = 0.0, norm_ahead: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
          ) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1).  With
@@ -83,7 +93,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
     if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, 1 if accumulate else 0,
+         1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, _gate_pointer(gate), 1 if accumulate else 0,
          None if row_sumsq is None else row_sumsq.data_ptr(), 0 if row_sumsq is None else row_sumsq.shape[-1], row_width,
          float(row_eps), *_norm_ahead_pointers(norm_ahead, M, N), error_flag(x.device).data_ptr(), ops._stream())
     return out
@@ -102,7 +112,7 @@ def _norm_ahead_pointers(norm_ahead, M: int, N: int):
 
 
 def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: int = 1, max_clusters: int = 0,
-              swiglu: bool = False, accumulate: bool = False, row_sumsq: Optional[torch.Tensor] = None,
+              swiglu: bool = False, accumulate: bool = False, row_sumsq: Optional[torch.Tensor] = None, gate=None,
               row_width: int = 0, row_eps: float = 0.0,
               norm_ahead: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T on pairs of CTAs (cta_group::2), tiles of 256 x 256; float32 partial sums
@@ -115,7 +125,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: in
     if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05_pair: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05_pair", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         splits, max_clusters, 1 if swiglu else 0, 1 if accumulate else 0,
+         splits, max_clusters, 1 if swiglu else 0, _gate_pointer(gate), 1 if accumulate else 0,
          None if row_sumsq is None else row_sumsq.data_ptr(), 0 if row_sumsq is None else row_sumsq.shape[-1], row_width,
          float(row_eps), *_norm_ahead_pointers(norm_ahead, M, N), error_flag(x.device).data_ptr(), ops._stream())
     return out

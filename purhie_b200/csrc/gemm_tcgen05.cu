@@ -50,6 +50,10 @@ struct GemmParams {
     int swapped;
     int accumulate;      // 1: out (float32, plain orientation, one split) += the product: the residual sum in the epilogue
     int swiglu;          // 1: columns are (gate, up) pairs; out[a, j] = silu(D[a, 2j]) * D[a, 2j + 1] (plain orientation)
+    // the gate's family: 0 silu(g) * u; 1 clamped swish: g' = min(g, limit), u' = clamp(u, -limit, limit),
+    // g' * sigmoid(alpha * g') * (u' + shift)
+    int gate_kind;
+    float gate_alpha, gate_limit, gate_shift;
     long long ld;        // row length of out
     long long split_stride;
     // A factor per token that the norm in front left out of the activations, rsqrt(sum over the chunks of
@@ -203,6 +207,14 @@ __device__ __forceinline__ float plain_row_factor(const GemmParams& p, int a) {
     return rsqrtf(s / (float)p.row_width + p.row_eps);
 }
 
+// The gated activation of a (gate, up) pair, by the family the parameters name.
+__device__ __forceinline__ float gate_times(const GemmParams& p, float g, float u) {
+    if (p.gate_kind == 0) return g / (1.0f + __expf(-g)) * u;
+    g = fminf(g, p.gate_limit);
+    u = fminf(fmaxf(u, -p.gate_limit), p.gate_limit);
+    return g / (1.0f + __expf(-p.gate_alpha * g)) * (u + p.gate_shift);
+}
+
 // One chunk of CH accumulator columns of row a, starting at column b0 + c of the tile, to its place in out.
 template <int CH>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t* r, int a, int b0, int c, size_t split_off) {
@@ -214,7 +226,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t*
 #pragma unroll
         for (int j = 0; j < CH / 2; ++j) {
             const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-            h[j] = g / (1.0f + __expf(-g)) * u;
+            h[j] = gate_times(p, g, u);
         }
         const bool full_chunk = (b0 + c + CH <= p.rows_b);
         if (p.out_bf16) {
@@ -395,7 +407,7 @@ __device__ __forceinline__ void store_chunk_swapped_swiglu(const GemmParams& p, 
         const float mine = __uint_as_float(r[j]);
         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
         if (writer && b0 + c + j < p.rows_b) {
-            const float h = mine / (1.0f + __expf(-mine)) * other;
+            const float h = gate_times(p, mine, other);
             const size_t at = (size_t)(b0 + c + j) * p.ld + (size_t)(a >> 1);
             if (p.out_bf16) ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(h);
             else ((float*)p.out)[at] = h;
@@ -424,7 +436,7 @@ __device__ __forceinline__ void store_chunk_swapped_bf16(const GemmParams& p, ui
             const float m0 = __uint_as_float(r[j]), m1 = __uint_as_float(r[j + 1]);
             const float got = __shfl_xor_sync(0xffffffffu, odd ? m0 : m1, 1);
             const float gate = odd ? got : m0, up = odd ? m1 : got;
-            buf[(j + odd) * 16 + (lane >> 1)] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+            buf[(j + odd) * 16 + (lane >> 1)] = __float2bfloat16_rn(gate_times(p, gate, up));
         }
     } else {
 #pragma unroll
@@ -730,9 +742,8 @@ __device__ __forceinline__ void put_chunk(unsigned char* box, int lane, int chun
     *(uint4*)(box + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
         make_uint4(*(const uint32_t*)&a, *(const uint32_t*)&b, *(const uint32_t*)&c, *(const uint32_t*)&d);
 }
-__device__ __forceinline__ float silu_times(uint32_t g_bits, uint32_t u_bits, float f) {
-    const float g = __uint_as_float(g_bits) * f, u = __uint_as_float(u_bits) * f;
-    return g / (1.0f + __expf(-g)) * u;
+__device__ __forceinline__ float silu_times(const GemmParams& p, uint32_t g_bits, uint32_t u_bits, float f) {
+    return gate_times(p, __uint_as_float(g_bits) * f, __uint_as_float(u_bits) * f);
 }
 __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -911,10 +922,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                             for (int j = 0; j < 2; ++j)
                                 put_chunk(box, lane, 2 * k + j,
-                                          silu_times(r[16 * j], r[16 * j + 1], row_f), silu_times(r[16 * j + 2], r[16 * j + 3], row_f),
-                                          silu_times(r[16 * j + 4], r[16 * j + 5], row_f), silu_times(r[16 * j + 6], r[16 * j + 7], row_f),
-                                          silu_times(r[16 * j + 8], r[16 * j + 9], row_f), silu_times(r[16 * j + 10], r[16 * j + 11], row_f),
-                                          silu_times(r[16 * j + 12], r[16 * j + 13], row_f), silu_times(r[16 * j + 14], r[16 * j + 15], row_f));
+                                          silu_times(p, r[16 * j], r[16 * j + 1], row_f), silu_times(p, r[16 * j + 2], r[16 * j + 3], row_f),
+                                          silu_times(p, r[16 * j + 4], r[16 * j + 5], row_f), silu_times(p, r[16 * j + 6], r[16 * j + 7], row_f),
+                                          silu_times(p, r[16 * j + 8], r[16 * j + 9], row_f), silu_times(p, r[16 * j + 10], r[16 * j + 11], row_f),
+                                          silu_times(p, r[16 * j + 12], r[16 * j + 13], row_f), silu_times(p, r[16 * j + 14], r[16 * j + 15], row_f));
                         } else {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
@@ -1144,7 +1155,7 @@ const char* row_ops_refused(const float* row_sumsq, int row_chunks, int row_widt
 // norm_rows (bfloat16 [M, N]), norm_sumsq (float32 [M, 2 * ceil(N / 256)]): with accumulate, what the norm after this
 // addition needs (GemmParams).  All may be null.
 PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                        int splits, int max_clusters, int swiglu, int accumulate,
+                                        int splits, int max_clusters, int swiglu, const float* gate, int accumulate,
                                         const float* row_sumsq, int row_chunks, int row_width, float row_eps,
                                         const float* norm_weight, void* norm_rows, float* norm_sumsq, int* error_flag,
                                         cudaStream_t stream) {
@@ -1166,7 +1177,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     GemmParams p;
     p.rows_a = M; p.rows_b = N; p.K = K;
     p.a_tiles = 0; p.b_tiles = (N + PAIR_BN - 1) / PAIR_BN; p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.gate_kind = gate ? 1 : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
@@ -1184,14 +1195,15 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
 
 // out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
 // side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).
-// swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue
+// swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue;
+// gate (three floats on the host: alpha, limit, shift; null: the silu gate) makes it the clamped swish of GemmParams
 // (the formula of src/gpu_ops.hip:103-114 in the reference).
 // accumulate: out (float32, plain orientation, one split, no activation) += the product.
 // row_sumsq [M][row_chunks] (or null), row_width, row_eps: the activations lack a factor per token, see GemmParams;
 // taken by the swapped orientation with bfloat16 output, and by the plain orientation with tiles of 256 columns.
 // norm_weight, norm_rows, norm_sumsq: as in the pair kernel (plain orientation, block_n 256, accumulate).
 PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                   int swapped, int block_n, int splits, int max_ctas, int swiglu, int accumulate,
+                                   int swapped, int block_n, int splits, int max_ctas, int swiglu, const float* gate, int accumulate,
                                    const float* row_sumsq, int row_chunks, int row_width, float row_eps,
                                    const float* norm_weight, void* norm_rows, float* norm_sumsq,
                                    int* error_flag, cudaStream_t stream) {
@@ -1227,7 +1239,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
     p.a_tiles = (rows_a + BM - 1) / BM; p.b_tiles = (rows_b + block_n - 1) / block_n;
     p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.gate_kind = gate ? 1 : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;

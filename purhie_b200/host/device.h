@@ -145,9 +145,9 @@ struct FlashKernels {
     const char* (*last_error)(void);
 };
 struct GemmKernels {
-    int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, const float*, int, int, float,
-                const float*, void*, float*, int*, cudaStream_t);
-    int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, const float*, int, int, float,
+    int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, const float*, int, const float*, int, int,
+                float, const float*, void*, float*, int*, cudaStream_t);
+    int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, const float*, int, const float*, int, int, float,
                      const float*, void*, float*, int*, cudaStream_t);
     const char* (*last_error)(void);
 };

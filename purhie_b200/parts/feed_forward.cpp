@@ -46,13 +46,15 @@ public:
 
     // bfloat16: the gate/up product's epilogue applies the norm's factor per row before the activation
     bool takes_unscaled_rows(const StepContext& ctx) const override {
-        return compute_dtype == DType::BF16 && gate_.kind == 0 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
+        return compute_dtype == DType::BF16 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
     }
 
     Addend forward(const Tensor& x, StepContext& ctx) override {
         const int T = ctx.T;
-        // the products' own epilogue knows the silu gate; any other gate is a kernel behind the product
-        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, gate_.kind == 0, nullptr, &ctx.row_scale);
+        // where the tensor-core product runs, its epilogue applies the gate (either family); else a kernel behind it does
+        const float gate_constants[3] = {gate_.alpha, gate_.limit, gate_.shift};
+        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, true, nullptr, &ctx.row_scale, nullptr,
+                             gate_.kind ? gate_constants : nullptr);
         Tensor act;
         if (gu.activated) act = gu.tensor;
         else {

@@ -122,15 +122,16 @@ void Linear::into(const Tensor& x_in, StepContext& ctx, Tensor out, int rows) co
     const GemmKernels& g = gemm_kernels();
     const GemmPlan p = plan_gemm(M, N, K, sm_count(), false, false);
     if (p.pair)
-        QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, 1, 0, 0, 0, nullptr, 0, 0, 0.0f, nullptr, nullptr,
-                                 nullptr, ctx.gemm_error, ctx.stream));
+        QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, 1, 0, 0, nullptr, 0, nullptr, 0, 0, 0.0f, nullptr,
+                                 nullptr, nullptr, ctx.gemm_error, ctx.stream));
     else
-        QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, 1, 0, 0, 0, nullptr, 0, 0, 0.0f,
-                            nullptr, nullptr, nullptr, ctx.gemm_error, ctx.stream));
+        QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, 1, 0, 0, nullptr, 0, nullptr, 0, 0,
+                            0.0f, nullptr, nullptr, nullptr, ctx.gemm_error, ctx.stream));
 }
 
 Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
-                          bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale, NormAhead* ahead) const {
+                          bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale, NormAhead* ahead,
+                          const float* gate) const {
     const int M = rows, N = (int)weight_.shape[0], K = (int)weight_.shape[1];
     Workspace& ws = *ctx.workspace;
     const CoreKernels& core = core_kernels();
@@ -172,10 +173,10 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
             ahead_weight = work_ahead->weight; ahead_rows = work_ahead->rows.data; ahead_sumsq = sums.as<float>();
         }
         if (p.pair)
-            QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, splits, 0, swiglu, accumulate, sumsq, chunks,
+            QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, splits, 0, swiglu, gate, accumulate, sumsq, chunks,
                                      width, eps, ahead_weight, ahead_rows, ahead_sumsq, ctx.gemm_error, ctx.stream));
         else
-            QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, splits, 0, swiglu,
+            QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, splits, 0, swiglu, gate,
                                 accumulate, sumsq, chunks, width, eps, ahead_weight, ahead_rows, ahead_sumsq, ctx.gemm_error,
                                 ctx.stream));
     };

@@ -908,3 +908,26 @@ def test_decode_attention_sees_the_key_written_by_the_kernel_in_front(ctx, split
         p = torch.softmax((K[:, kv] @ q[r, h].double()) * scale, 0)
         ref.append(p @ V[:, kv])
     assert rel(out[r].double(), torch.cat(ref)) < 5e-3
+
+
+@pytest.mark.parametrize("form,M,N,K", [("plain", 200, 512, 192), ("pair", 512, 768, 256), ("few", 8, 384, 320), ("few", 40, 256, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_clamped_gate_in_every_epilogue(form, M, N, K, out_dtype):
+    """The other gate of the fused epilogue: g' = min(g, limit), u' = clamp(u, -limit, limit),
+    g' sigmoid(alpha g') (u' + shift), in the plain, the paired and the few-token orientation, with sums large
+    enough that both clamps work."""
+    from purhie_b200.csrc import gemm100
+    alpha, limit, shift = 1.702, 0.75, 1.0
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=31), rnd(N, K, dtype=torch.bfloat16, seed=32, scale=0.2)
+    out = torch.full((M, N // 2), float("nan"), dtype=out_dtype, device=DEV)
+    if form == "pair":
+        gemm100.gemm_pair(x, w, out, swiglu=True, gate=(alpha, limit, shift))
+    else:
+        gemm100.gemm(x, w, out, swapped=form == "few", block_n=256 if form == "plain" else 64, swiglu=True, gate=(alpha, limit, shift))
+    gemm100.check_errors(DEV)
+    y = x.double() @ w.double().T
+    g, u = y[:, 0::2], y[:, 1::2]
+    assert (g > limit).any() and (u < -limit).any() and (u > limit).any()
+    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    assert not torch.isnan(out).any()
+    assert rel(out, g / (1 + torch.exp(-alpha * g)) * (u + shift)) < (3e-5 if out_dtype == torch.float32 else 6e-3)
