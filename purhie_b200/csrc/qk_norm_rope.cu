@@ -38,6 +38,15 @@ __device__ __forceinline__ float row_factor(const RowFactor& rf, int t) {
 }
 constexpr int MAX_D = 512;
 
+// A pair (a, b) turned by an angle with cosine c and sine s: (a c - b s, b c + a s), each as one product rounded and
+// one fused multiply-add, written out so that every kernel of this file gives the same bits for the same pair.
+// The sum of squares of four values, the same roundings wherever it is taken.
+__device__ __forceinline__ float squares4(float a, float b, float c, float d) {
+    return __fmaf_rn(d, d, __fmaf_rn(c, c, __fmaf_rn(b, b, __fmul_rn(a, a))));
+}
+__device__ __forceinline__ float turn_first(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
+__device__ __forceinline__ float turn_second(float a, float b, float c, float s) { return __fmaf_rn(a, s, __fmul_rn(b, c)); }
+
 template <typename TI, typename TQ, typename TKV>
 __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long long split_stride,
                                     const float* __restrict__ bias, const float* __restrict__ q_w,
@@ -110,11 +119,11 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
             if (interleaved) {
                 const int j = d >> 1;
                 const float c = cs[j], s = cs[half + j];
-                v = (d & 1) ? row[d - 1] * s + row[d] * c : row[d] * c - row[d + 1] * s;
+                v = (d & 1) ? turn_second(row[d - 1], row[d], c, s) : turn_first(row[d], row[d + 1], c, s);
             } else {
                 const int j = d < half ? d : d - half;
                 const float c = cs[j], s = cs[half + j];
-                v = d < half ? row[d] * c - row[d + half] * s : row[d - half] * s + row[d] * c;
+                v = d < half ? turn_first(row[d], row[d + half], c, s) : turn_second(row[d - half], row[d], c, s);
             }
         }
         outv[i] = v;
@@ -166,7 +175,8 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
                                          int max_pos, const int32_t* __restrict__ positions,
                                          const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                          TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                         int page_size, int HQ, int HKV, RowFactor rf) {
+                                         int page_size, int HQ, int HKV, RowFactor rf, int interleaved,
+                                         float* __restrict__ v_first, const float* __restrict__ v_lambda, int v_mode) {
     constexpr int D = 128;
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,10 +192,18 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
     if (cos_sin) {
         int pos = positions[t];
         pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-        const int j = (lane & 15) * 4;                       // pair index of this lane's first dimension
-        c = ld4(cos_sin + (size_t)pos * D + j);
-        sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
+        if (interleaved) {                                   // pairs (2i, 2i + 1): this lane's two pairs are 2 lane, 2 lane + 1
+            const float2 cc = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * D + 2 * lane);
+            const float2 ss = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * D + 64 + 2 * lane);
+            c = make_float4(cc.x, cc.y, 0.0f, 0.0f);
+            sn = make_float4(ss.x, ss.y, 0.0f, 0.0f);
+        } else {
+            const int j = (lane & 15) * 4;                   // pair index of this lane's first dimension
+            c = ld4(cos_sin + (size_t)pos * D + j);
+            sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
+        }
     }
+    const float lam = v_mode == 2 ? *v_lambda : 0.0f;
     const float4 gq = q_w ? ld4(q_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
     const float4 gk = k_w ? ld4(k_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
     pdl_wait();
@@ -220,24 +238,38 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
         if (!is_q && !is_k) {
             if (slot < 0) continue;
             const int h = head - HQ - HKV;
+            if (v_mode) {                                    // the step's first values: kept, or blended in
+                float* first = v_first + ((size_t)t * HKV + h) * D + d0;
+                if (v_mode == 1) st4(first, x);
+                else {
+                    const float4 f = ld4(first);
+                    x = make_float4((1.0f - lam) * x.x + lam * f.x, (1.0f - lam) * x.y + lam * f.y, (1.0f - lam) * x.z + lam * f.z,
+                                    (1.0f - lam) * x.w + lam * f.w);
+                }
+            }
             st4(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, x);
             continue;
         }
         const float* w = is_q ? q_w : k_w;
         if (w) {
-            const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+            const float ss = warp_sum(squares4(x.x, x.y, x.z, x.w));
             const float inv = rsqrtf(ss / (float)D + eps);
             const float4 g = is_q ? gq : gk;
             x.x = x.x * inv * g.x; x.y = x.y * inv * g.y; x.z = x.z * inv * g.z; x.w = x.w * inv * g.w;
         }
-        if (cos_sin) {
+        if (cos_sin && interleaved) {
+            x = make_float4(turn_first(x.x, x.y, c.x, sn.x), turn_second(x.x, x.y, c.x, sn.x), turn_first(x.z, x.w, c.y, sn.y),
+                            turn_second(x.z, x.w, c.y, sn.y));
+        } else if (cos_sin) {
             float4 o;
             o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
             o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
             if (lane < 16) {       // first half: a cos - b sin
-                x.x = x.x * c.x - o.x * sn.x; x.y = x.y * c.y - o.y * sn.y; x.z = x.z * c.z - o.z * sn.z; x.w = x.w * c.w - o.w * sn.w;
+                x = make_float4(turn_first(x.x, o.x, c.x, sn.x), turn_first(x.y, o.y, c.y, sn.y), turn_first(x.z, o.z, c.z, sn.z),
+                                turn_first(x.w, o.w, c.w, sn.w));
             } else {               // second half: a sin + b cos (a is the partner)
-                x.x = o.x * sn.x + x.x * c.x; x.y = o.y * sn.y + x.y * c.y; x.z = o.z * sn.z + x.z * c.z; x.w = o.w * sn.w + x.w * c.w;
+                x = make_float4(turn_second(o.x, x.x, c.x, sn.x), turn_second(o.y, x.y, c.y, sn.y), turn_second(o.z, x.z, c.z, sn.z),
+                                turn_second(o.w, x.w, c.w, sn.w));
             }
         }
         if (is_q) {
@@ -278,8 +310,10 @@ __device__ __forceinline__ float4 shfl4(const float4& v, int m) {
 }
 // first half of the head: a cos - b sin; second half: a sin + b cos with a the partner
 __device__ __forceinline__ float4 rotate4(const float4& x, const float4& o, const float4& c, const float4& sn, bool first) {
-    if (first) return make_float4(x.x * c.x - o.x * sn.x, x.y * c.y - o.y * sn.y, x.z * c.z - o.z * sn.z, x.w * c.w - o.w * sn.w);
-    return make_float4(o.x * sn.x + x.x * c.x, o.y * sn.y + x.y * c.y, o.z * sn.z + x.z * c.z, o.w * sn.w + x.w * c.w);
+    if (first) return make_float4(turn_first(x.x, o.x, c.x, sn.x), turn_first(x.y, o.y, c.y, sn.y), turn_first(x.z, o.z, c.z, sn.z),
+                                  turn_first(x.w, o.w, c.w, sn.w));
+    return make_float4(turn_second(o.x, x.x, c.x, sn.x), turn_second(o.y, x.y, c.y, sn.y), turn_second(o.z, x.z, c.z, sn.z),
+                       turn_second(o.w, x.w, c.w, sn.w));
 }
 
 template <typename TI, typename TQ, typename TKV, int ITERS>
@@ -289,10 +323,12 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
                                               int max_pos, const int32_t* __restrict__ positions,
                                               const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                               TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                              int page_size, int HQ, int HKV, RowFactor rf) {
+                                              int page_size, int HQ, int HKV, RowFactor rf, int interleaved,
+                                              float* __restrict__ v_first, const float* __restrict__ v_lambda, int v_mode) {
     constexpr int D = 128;
     pdl_launch_dependents();
     pdl_wait();
+    const float lam = v_mode == 2 ? *v_lambda : 0.0f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, l16 = lane & 15;
     const int head0 = (blockIdx.y * WARPS + warp) * 2 * ITERS + half;      // this half-warp's heads: head0, head0 + 2, ...
@@ -318,10 +354,15 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
     if (cos_sin) {
         int pos = positions[t];
         pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-        const int j = (l16 & 7) * 8;                         // pair index of this lane's first dimension
         const float* row = cos_sin + (size_t)pos * D;
-        c0 = ld4(row + j); c1 = ld4(row + j + 4);
-        s0 = ld4(row + 64 + j); s1 = ld4(row + 64 + j + 4);
+        if (interleaved) {                                   // pairs (2i, 2i + 1): this lane's four pairs start at 4 l16
+            c0 = ld4(row + 4 * l16);
+            s0 = ld4(row + 64 + 4 * l16);
+        } else {
+            const int j = (l16 & 7) * 8;                     // pair index of this lane's first dimension
+            c0 = ld4(row + j); c1 = ld4(row + j + 4);
+            s0 = ld4(row + 64 + j); s1 = ld4(row + 64 + j + 4);
+        }
     }
     const bool first = l16 < 8;
 #pragma unroll
@@ -339,8 +380,8 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
         const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
         const float* w = is_q ? q_w : k_w;
         // sum of squares: the two four-element groups of the lane apart over the half-warp, then together
-        float p0 = x.a.x * x.a.x + x.a.y * x.a.y + x.a.z * x.a.z + x.a.w * x.a.w;
-        float p1 = x.b.x * x.b.x + x.b.y * x.b.y + x.b.z * x.b.z + x.b.w * x.b.w;
+        float p0 = squares4(x.a.x, x.a.y, x.a.z, x.a.w);
+        float p1 = squares4(x.b.x, x.b.y, x.b.z, x.b.w);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
             p0 += __shfl_xor_sync(0xffffffffu, p0, o);
@@ -358,11 +399,27 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
         if (!is_q && !is_k) {
             if (slot >= 0) {
                 const int h = head - HQ - HKV;
+                if (v_mode) {                                // the step's first values: kept, or blended in
+                    float* fp = v_first + ((size_t)t * HKV + h) * D + d0;
+                    if (v_mode == 1) st8(fp, x);
+                    else {
+                        const F8 f = ld8(fp);
+                        const float k = 1.0f - lam;
+                        x.a = make_float4(k * x.a.x + lam * f.a.x, k * x.a.y + lam * f.a.y, k * x.a.z + lam * f.a.z, k * x.a.w + lam * f.a.w);
+                        x.b = make_float4(k * x.b.x + lam * f.b.x, k * x.b.y + lam * f.b.y, k * x.b.z + lam * f.b.z, k * x.b.w + lam * f.b.w);
+                    }
+                }
                 st8(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, x);
             }
             continue;
         }
-        if (cos_sin) {
+        if (cos_sin && interleaved) {
+            const float4 a = y.a, b = y.b;
+            y.a = make_float4(turn_first(a.x, a.y, c0.x, s0.x), turn_second(a.x, a.y, c0.x, s0.x), turn_first(a.z, a.w, c0.y, s0.y),
+                              turn_second(a.z, a.w, c0.y, s0.y));
+            y.b = make_float4(turn_first(b.x, b.y, c0.z, s0.z), turn_second(b.x, b.y, c0.z, s0.z), turn_first(b.z, b.w, c0.w, s0.w),
+                              turn_second(b.z, b.w, c0.w, s0.w));
+        } else if (cos_sin) {
             y.a = rotate4(y.a, oa, c0, s0, first);
             y.b = rotate4(y.b, ob, c1, s1, first);
         }
@@ -400,7 +457,7 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
     if (T == 0) return PH_OK;
     const RowFactor rf = {row_sumsq, row_chunks, row_width, row_eps};
     dim3 grid(T, (HQ + 2 * HKV + WARPS - 1) / WARPS);
-    const bool fast = D == 128 && DV == D && v_mode == 0 && (!cos_sin || (n_rot == 128 && !interleaved)) && split_stride % 4 == 0 &&
+    const bool fast = D == 128 && DV == D && (!cos_sin || n_rot == 128) && split_stride % 4 == 0 && (((uintptr_t)v_first) & 15) == 0 &&
                       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)bias |
                         (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
     if (fast) {
@@ -413,11 +470,13 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
         if (many)                                                                                                   \
             launch_overlapped(qk_norm_rope_d128_wide_kernel<TI, TQ, TKV, 3>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
                               splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
-                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf); \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf, \
+                              interleaved, v_first, v_lambda, v_mode);                                               \
         else                                                                                                        \
             launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV, 1>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
                               splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
-                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf); \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf, \
+                              interleaved, v_first, v_lambda, v_mode);                                               \
     } while (0)
         PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_FAST(TI, TQ, TKV))));
 #undef LAUNCH_FAST

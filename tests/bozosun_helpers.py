@@ -66,6 +66,14 @@ CONFIG_C = config(128, 200, [
 ], mult=0.3, eps=1e-6, embed_scale=11.0)
 
 
+# heads of 128 rotated over their whole width, values as wide, mixing: what the vector rotary kernels and the tcgen05
+# prompt attention take
+CONFIG_D = config(64, 50, [
+    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}), v_mix=True), dense(48, 2.0)),
+    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}), v_mix=True), None),
+], mult=0.7, eps=1e-5, embed_scale=3.0)
+
+
 def to_bf16_bytes(a):
     """Round float32 to bfloat16 (nearest even) and return the bytes."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)

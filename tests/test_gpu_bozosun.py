@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from plain import bozosun_plain as P
-from bozosun_helpers import (CONFIG_A, CONFIG_B, CONFIG_C, YARN, attention, bf16_round, config, dense, draw_weights, make_folder,
+from bozosun_helpers import (CONFIG_A, CONFIG_B, CONFIG_C, CONFIG_D, YARN, attention, bf16_round, config, dense, draw_weights, make_folder,
                              mamba, moe, rot, steady_routing, tokens)
 
 pytestmark = pytest.mark.gpu
@@ -155,6 +155,22 @@ def test_a_prompt_of_many_pairs_goes_through_the_tiled_expert_products(models, n
     close(out[1:301], ref[:300], TOL[dtype])
     close(out[:1], ref[5:6], TOL[dtype])
     close(out[301:], ref[9:11], TOL[dtype])
+    eng.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_heads_of_128_go_through_the_vector_rotary_kernels(tmp_path, dtype):
+    """Interleaved pairs and the value blend in the kernels that hold four or eight dimensions of a head per lane: a
+    short prompt with decoding (the few-token kernel), and a prompt long enough for the many-token one."""
+    w = draw_weights(CONFIG_D, 5)
+    folder = make_folder(tmp_path, CONFIG_D, w, "F32" if dtype == "float32" else "BF16")
+    eng = engine_for(folder, dtype, page_size=16, max_tokens=4608)
+    toks = tokens(70, CONFIG_D["vocab"], 2)
+    close(run_cut(eng, "short", toks, [40] + [1] * 20), P.forward(CONFIG_D, f64(w), toks), TOL[dtype])
+    toks = tokens(4200, CONFIG_D["vocab"], 3)
+    ref = P.forward(CONFIG_D, f64(w), toks)
+    got = run_cut(eng, "long", toks, [4100, 2, 1])
+    close(got, ref, TOL[dtype])
     eng.close()
 
 
