@@ -107,7 +107,7 @@ DESIGN_SIZES = {
 
 
 def bozosun_config(z):
-    rot = {"base": 1e6, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 5e5, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 4096, "fast": 24.0, "slow": 2.0}}
     att = lambda: {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
                                                   "rot": rot, "scale": z["dim"] ** -0.5, "v_mix": True}}
     ssm = lambda: {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}}

@@ -60,17 +60,17 @@ CONFIG_B = config(40, 70, [
 
 # head size 64 with values as wide: what the tensor-core attention kernels take in bfloat16
 CONFIG_C = config(128, 200, [
-    (attention(4, 2, 64, 64, rot(64, 1e6, {"factor": 4.0, "original": 128, "fast": 32.0, "slow": 1.0})), dense(256, 1.5)),
-    (mamba(256, 16, 8, 4), moe(64, 1.0, 8, 2)),
-    (attention(4, 2, 64, 64, rot(32, 1e6, None)), moe(64, 1.0, 8, 2)),
-], mult=0.3, eps=1e-6, embed_scale=11.0)
+    (attention(4, 2, 64, 64, rot(64, 5e5, {"factor": 3.0, "original": 128, "fast": 24.0, "slow": 1.5})), dense(256, 1.75)),
+    (mamba(256, 16, 8, 4), moe(64, 0.9, 8, 2)),
+    (attention(4, 2, 64, 64, rot(32, 5e5, None)), moe(64, 0.9, 8, 2)),
+], mult=0.35, eps=1e-6, embed_scale=11.0)
 
 
 # heads of 128 rotated over their whole width, values as wide, mixing: what the vector rotary kernels and the tcgen05
 # prompt attention take
 CONFIG_D = config(64, 50, [
-    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}), v_mix=True), dense(48, 2.0)),
-    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}), v_mix=True), None),
+    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 6.0, "original": 1024, "fast": 20.0, "slow": 2.0}), v_mix=True), dense(48, 2.0)),
+    (attention(2, 1, 128, 128, rot(128, 1e5, {"factor": 6.0, "original": 1024, "fast": 20.0, "slow": 2.0}), v_mix=True), None),
 ], mult=0.7, eps=1e-5, embed_scale=3.0)
 
 
