@@ -75,3 +75,14 @@ def test_other_architectures_are_still_read_by_their_list_of_names():
     assert ModelConfig.from_dict(TINY_A).architecture == "Qwen3ForCausalLM"
     with pytest.raises(ConfigError):
         ModelConfig.from_dict({"vocab": 3})
+
+
+def test_a_random_model_folder_of_this_design_is_written_and_passes_the_folder_check(tmp_path):
+    from purhie_b200.config import load_config
+    from purhie_b200.weights import check_model_folder, list_tensors, write_random_model
+    write_random_model(str(tmp_path), CONFIG_B, seed=3, std=0.05, scale_low=0.8, scale_high=1.2, dtype="bfloat16")
+    check_model_folder(str(tmp_path))
+    names = {t["name"]: t for t in list_tensors(str(tmp_path))}
+    assert set(names) == set(expected_tensors(CONFIG_B))
+    assert names["l4.mix.vmix"]["shape"] == [] and names["l0.mix.A_log"]["shape"] == [56, 20]
+    assert load_config(str(tmp_path)).to_dict()["layers"] == CONFIG_B["layers"]
