@@ -174,6 +174,25 @@ def test_heads_of_128_go_through_the_vector_rotary_kernels(tmp_path, dtype):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_of_state_space_layers_alone_keeps_no_pages(tmp_path, dtype):
+    """No attention anywhere: the cache manager has state slots and not one page group; a convolution of one tap
+    keeps no inputs; a layer's feed-forward may be missing."""
+    cfg = config(24, 40, [(mamba(40, 8, 4, 1), dense(32, 1.0)), (mamba(32, 16, 8, 2), None), (mamba(40, 8, 4, 6), moe(8, 1.5, 4, 2))],
+                 mult=0.6, eps=1e-4, embed_scale=2.0)
+    w = draw_weights(cfg, 17)
+    if dtype == "bfloat16":
+        w = steady_routing(cfg, w, 1)
+    folder = make_folder(tmp_path, cfg, w, "F32" if dtype == "float32" else "BF16")
+    eng = engine_for(folder, dtype, max_requests=2)
+    assert eng.info()["total_pages"] == []
+    toks = tokens(210, cfg["vocab"], 6)
+    ref = P.forward(cfg, f64(w), toks)
+    close(run_cut(eng, "whole", toks, []), ref, TOL[dtype])
+    close(run_cut(eng, "cut", toks, [3, 1, 2, 195, 1, 1]), ref, TOL[dtype])
+    eng.close()
+
+
 def test_long_decoding_keeps_its_state(models):
     folder, cfg, w = models["A"]
     eng = engine_for(folder, "float32", max_tokens=256)
