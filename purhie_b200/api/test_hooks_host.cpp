@@ -28,7 +28,16 @@ std::vector<CacheNeed> needs_from_json(const Json& list) {
     std::vector<CacheNeed> needs;
     for (const Json& n : list.items()) {
         const std::string kind = n.get_string("kind", "none");
-        if (kind == "pages") needs.push_back(CacheNeed::pages((int)n.at("kv_heads").as_int(), (int)n.at("head_dim").as_int(), (int)n.get_int("window", 0), (int)n.get_int("value_dim", 0)));
+        if (kind == "pages") {
+            CacheNeed need = CacheNeed::pages((int)n.at("kv_heads").as_int(), (int)n.at("head_dim").as_int(), (int)n.get_int("window", 0),
+                                              (int)n.get_int("value_dim", 0), (int)n.get_int("chunk", 0));
+            if (const Json* st = n.find("state")) {          // a mixer of pages that keeps a state as well
+                std::vector<int64_t> shape;
+                for (const Json& d : st->items()) shape.push_back(d.as_int());
+                need = CacheNeed::both(need, CacheNeed::state(shape));
+            }
+            needs.push_back(need);
+        }
         else if (kind == "state") {
             std::vector<int64_t> shape;
             for (const Json& d : n.at("shape").items()) shape.push_back(d.as_int());
@@ -53,6 +62,7 @@ Json cache_info(const CacheManager& c) {
         Json gj = Json::object();
         gj.set("entries", ints(g.entries));
         gj.set("window", g.window ? Json(g.window) : Json());
+        gj.set("chunk", g.chunk);
         gj.set("kv_heads", g.kv_heads);
         gj.set("head_dim", g.head_dim);
         gj.set("value_dim", g.value_dim);

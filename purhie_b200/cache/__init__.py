@@ -51,12 +51,15 @@ class CacheNeed:
     window: Optional[int] = None          # pages: None keeps all keys, W keeps the last W positions
     state_shape: Tuple[int, ...] = ()
     value_dim: int = 0                    # pages: width of a value row where it differs from a key row's (0: head_dim)
+    chunk: int = 0                        # pages: C > 0 keeps the keys of the block of C positions the next position is in
 
     @staticmethod
-    def pages(kv_heads: int, head_dim: int, window: Optional[int] = None, value_dim: int = 0) -> "CacheNeed":
+    def pages(kv_heads: int, head_dim: int, window: Optional[int] = None, value_dim: int = 0, chunk: int = 0,
+              state: Sequence[int] = ()) -> "CacheNeed":
+        """``state``: the shape of a state the same mixer keeps beside its pages (two mixers side by side)."""
         if window is not None and window < 1:
             raise ValueError("a window must hold at least one position")
-        return CacheNeed("pages", kv_heads, head_dim, window, value_dim=0 if value_dim == head_dim else value_dim)
+        return CacheNeed("pages", kv_heads, head_dim, window, tuple(state), 0 if value_dim == head_dim else value_dim, chunk)
 
     @staticmethod
     def state(shape: Sequence[int]) -> "CacheNeed":
@@ -64,8 +67,11 @@ class CacheNeed:
 
     def to_json(self) -> dict:
         if self.kind == "pages":
-            return {"kind": "pages", "kv_heads": self.kv_heads, "head_dim": self.head_dim, "window": self.window or 0,
-                    "value_dim": self.value_dim}
+            d = {"kind": "pages", "kv_heads": self.kv_heads, "head_dim": self.head_dim, "window": self.window or 0,
+                 "value_dim": self.value_dim, "chunk": self.chunk}
+            if self.state_shape:
+                d["state"] = list(self.state_shape)
+            return d
         if self.kind == "state":
             return {"kind": "state", "shape": list(self.state_shape)}
         return {"kind": "none"}

@@ -86,15 +86,15 @@ CacheManager::CacheManager(std::vector<CacheNeed> needs, int page_size, std::vec
     if (max_requests < 1) throw Error(kInvalidArg, "max_requests must be >= 1");
     for (int i = 0; i < (int)needs_.size(); i++) {
         const CacheNeed& need = needs_[i];
-        if (need.kind == CacheNeed::State) state_entries_.push_back(i);
+        if (need.has_state()) state_entries_.push_back(i);
         if (need.kind != CacheNeed::Pages) continue;
         int gi = -1;
         for (const PageGroup& g : groups_)
-            if (g.kv_heads == need.kv_heads && g.head_dim == need.head_dim && g.value_dim == need.v_dim() && g.window == need.window) gi = g.index;
+            if (g.kv_heads == need.kv_heads && g.head_dim == need.head_dim && g.value_dim == need.v_dim() && g.window == need.window && g.chunk == need.chunk) gi = g.index;
         if (gi < 0) {
             PageGroup g;
             g.index = gi = (int)groups_.size();
-            g.kv_heads = need.kv_heads; g.head_dim = need.head_dim; g.value_dim = need.v_dim(); g.window = need.window;
+            g.kv_heads = need.kv_heads; g.head_dim = need.head_dim; g.value_dim = need.v_dim(); g.window = need.window; g.chunk = need.chunk;
             groups_.push_back(std::move(g));
         }
         groups_[gi].entries.push_back(i);
@@ -161,8 +161,10 @@ void CacheManager::add_request(int64_t id) {
 }
 
 int CacheManager::first_needed_block(const PageGroup& g, int start) const {
-    if (!g.window) return 0;
-    return std::max(0, start - g.window + 1) / page_size_;
+    // the first position that the position `start` (and every later one) can still see
+    int first = g.window ? std::max(0, start - g.window + 1) : 0;
+    if (g.chunk) first = std::max(first, start / g.chunk * g.chunk);
+    return first / page_size_;
 }
 
 std::vector<int> CacheManager::pages_needed(int64_t id, int n_new) const {
@@ -224,7 +226,7 @@ void CacheManager::advance(int64_t id, int n_new) {
     if (!groups_.empty() && rc.length > (int)rc.tables[0].size() * page_size_)
         throw Error(kInvalidState, "request " + std::to_string(id) + " advanced past its reserved pages");
     for (PageGroup& g : groups_) {
-        if (!g.window) continue;
+        if (!g.window && !g.chunk) continue;
         std::vector<int>& table = rc.tables[g.index];
         const int keep_from = std::min(first_needed_block(g, rc.length), (int)table.size());
         std::vector<int> passed;
@@ -238,7 +240,7 @@ void CacheManager::advance(int64_t id, int n_new) {
 }
 
 bool CacheManager::can_rewind() const {
-    for (const PageGroup& g : groups_) if (g.window) return false;
+    for (const PageGroup& g : groups_) if (g.window || g.chunk) return false;
     return state_entries_.empty();
 }
 
@@ -319,7 +321,8 @@ CacheView CacheManager::view(int entry, int owner) const {
         v.page_stride = g.page_stride;
         v.page_size = page_size_;
         v.num_pages = g.allocator.num_pages();
-    } else if (need.kind == CacheNeed::State) {
+    }
+    if (need.has_state()) {
         std::vector<int64_t> shape = {max_requests_};
         shape.insert(shape.end(), need.state_shape.begin(), need.state_shape.end());
         auto it = state_.find(owner);

@@ -1,7 +1,8 @@
 // The cache manager: paged keys and values with a block table per request, and state slots.
 //
 // Each entry of a model's run order tells the manager what it needs (CacheNeed): pages holding all keys, pages
-// holding a window of them, a fixed-size state per request, or nothing.  Entries with the same page geometry
+// holding a window of them or the current block of a block mask, a fixed-size state per request (also beside
+// pages), or nothing.  Entries with the same page geometry
 // and the same policy form a group; a group has a pool of pages of its own, one page id addresses the keys and
 // values of all the group's entries (the reference's "one block, all layers" layout, src/kv_cache.h:1-14), and
 // every live request has one block table per group.  Pages go back to the pool when a request is released and,
@@ -59,7 +60,7 @@ private:
 
 struct PageGroup {
     int index = 0;
-    int kv_heads = 0, head_dim = 0, value_dim = 0, window = 0;      // value_dim: as CacheNeed::v_dim()
+    int kv_heads = 0, head_dim = 0, value_dim = 0, window = 0, chunk = 0;      // value_dim: as CacheNeed::v_dim()
     std::vector<int> entries;                      // run-order entries whose keys and values live in this group
     PageAllocator allocator;
     // [entries, pages, {K: kv_heads x page_size x head_dim, V: ... x value_dim}]: what one layer's attention reads lies
@@ -102,7 +103,7 @@ public:
     void unreserve(int64_t id);                    // give back the pages reserved beyond the request's length
     void advance(int64_t id, int n_new);           // the tokens are in the cache now; window groups give back what no later position sees
     void truncate(int64_t id, int length);         // forget everything from `length` on; not with windows or state
-    bool can_rewind() const;                       // no window group and no state entry
+    bool can_rewind() const;                       // no window or block group and no state entry
     void release(int64_t id);
 
     // ---- what a step needs

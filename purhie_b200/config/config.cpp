@@ -333,12 +333,14 @@ ModelSpec Qwen3Config::build_spec() const {
 }
 
 void register_bozosun_architecture();
+void register_sizizen_architecture();
 
 void register_builtin_architectures() {
     static std::once_flag once;
     std::call_once(once, [] {
         register_architecture("Qwen3ForCausalLM", Qwen3Config::read);
         register_bozosun_architecture();
+        register_sizizen_architecture();
     });
 }
 

@@ -4,7 +4,9 @@
 //
 // Values may have another width (DV) than keys (D); the output row of a head is DV wide.
 // One warp per (token row, query head).  The row at absolute position z of a request sees the cached
-// positions lo .. z, lo = max(0, z - window + 1) (window 0: lo = 0).  Keys are taken 32 at a time
+// positions lo .. z, lo = max(0, z - window + 1) (window 0: lo = 0); with a block mask (chunk > 0) it sees only
+// the positions of its own block of `chunk` positions counted from 0, lo = max(lo, floor(z / chunk) * chunk).
+// Keys are taken 32 at a time
 // starting from lo: each lane scores one key (the whole dot product in one lane, in d order), the warp
 // keeps a running maximum and sum (online softmax) and each lane owns the output dimensions d = lane,
 // lane + 32, ...  The order of every addition depends on (z, window) only, never on how the request was
@@ -27,7 +29,7 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
                                          const TKV* __restrict__ v_base, long long page_stride, int page_size,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
-                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV) {
+                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV, int chunk) {
     __shared__ float qs[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -35,7 +37,8 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
     const int t = (int)(item / HQ), h = (int)(item % HQ);
     const int g = h / (HQ / HKV);
     const int z = positions[t];
-    const int lo = (window > 0 && z - window + 1 > 0) ? z - window + 1 : 0;
+    int lo = (window > 0 && z - window + 1 > 0) ? z - window + 1 : 0;
+    if (chunk > 0 && z / chunk * chunk > lo) lo = z / chunk * chunk;
     const int32_t* table = block_table + (size_t)row_seg[t] * table_stride;
     const TQ* qr = q + ((size_t)t * HQ + h) * D;
     for (int d = lane; d < D; d += 32) qs[warp][d] = to_float<TQ>(qr[d]);
@@ -93,9 +96,9 @@ PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_bas
                                    long long page_stride, int page_size, const int32_t* block_table,
                                    int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
                                    int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
-                                   cudaStream_t stream) {
+                                   int chunk, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || T < 0 || HQ < 1 || HKV < 1 ||
-        D < 1 || page_size < 1 || window < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) ||
+        D < 1 || page_size < 1 || window < 0 || chunk < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) ||
         !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "attention_generic: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
     if (HQ % HKV) return fail(PH_ERR_ARG, "attention_generic: %d query heads are not a multiple of %d kv heads", HQ, HKV);
@@ -107,7 +110,7 @@ PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_bas
 #define LAUNCH(TQ, TKV, TO)                                                                                    \
     attention_generic_kernel<TQ, TKV, TO><<<blocks, WARPS * 32, 0, stream>>>(                                  \
         (const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, table_stride, \
-        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV)
+        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV, chunk)
     PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TO))));
 #undef LAUNCH
     return check_launch("attention_generic");

@@ -2,6 +2,7 @@
 // SwiGLU kernel reads them), with the gate's family as a parameter:
 //   kind 0 (silu):           out = g / (1 + exp(-g)) * u
 //   kind 1 (clamped swish):  g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(alpha * g') * (u' + shift)
+// and activations of one argument over plain rows (unary_act): kind 0 silu, kind 1 the square of relu.
 // The sums over split-K partial results and the activation are float32.
 #include "common.cuh"
 
@@ -53,7 +54,60 @@ __global__ void glu_vec_kernel(const TI* __restrict__ gu, int splits, long long 
     store4(out + q * 4, o);
 }
 
+__device__ __forceinline__ float unary(float x, int kind) {
+    if (kind == 0) return x / (1.0f + expf(-x));
+    x = fmaxf(x, 0.0f);
+    return x * x;
+}
+
+template <typename TI, typename TO>
+__global__ void unary_act_kernel(const TI* __restrict__ in, int splits, long long split_stride, TO* __restrict__ out, long long total,
+                                 int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    float x = 0.0f;
+    for (int s = 0; s < splits; ++s) x += to_float<TI>(in[(size_t)s * split_stride + idx]);
+    out[idx] = from_float<TO>(unary(x, kind));
+}
+
+template <typename TI, typename TO>
+__global__ void unary_act_vec_kernel(const TI* __restrict__ in, int splits, long long split_stride, TO* __restrict__ out, long long total4,
+                                     int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= total4) return;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = load4(in + (size_t)s * split_stride + q * 4);
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = unary(acc[i], kind);
+    store4(out + q * 4, acc);
+}
+
 }  // namespace
+
+PH_EXPORT int ph_unary_act(const void* in, int in_dtype, int splits, long long split_stride, void* out, int out_dtype, long long n,
+                           int kind, cudaStream_t stream) {
+    if (!in || !out || n < 0 || splits < 1 || kind < 0 || kind > 1 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "unary_act: bad arguments (n %lld, kind %d)", n, kind);
+    if (n == 0) return PH_OK;
+    if (n % 4 == 0 && split_stride % 4 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        const long long total4 = n / 4;
+        PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+            launch_overlapped(unary_act_vec_kernel<TI, TO>, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, stream, (const TI*)in,
+                              splits, split_stride, (TO*)out, total4, kind)));
+        return check_launch("unary_act");
+    }
+    PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+        launch_overlapped(unary_act_kernel<TI, TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const TI*)in, splits,
+                          split_stride, (TO*)out, n, kind)));
+    return check_launch("unary_act");
+}
 
 PH_EXPORT int ph_glu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out, int out_dtype, int T,
                      int FF, int kind, float alpha, float limit, float shift, cudaStream_t stream) {

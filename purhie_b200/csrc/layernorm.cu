@@ -3,7 +3,8 @@
 //     a = sum over the splits of add[s][t]                       (the output of a mixer or feed-forward)
 //     a = (a - mean(a)) / sqrt(var(a) + post_eps) * post_w + post_b      (when post_w is given: a norm on the addend)
 //     v = x[t] + add_scale * a                                   (stored back to x[t] when write_x)
-//     y = (v - mean(v)) / sqrt(var(v) + eps) * w + b             (when w is given)
+//     y = (v - mean(v)) / sqrt(var(v) + eps) * w + b             (when w is given; y = v when only y is: a part that
+//                                                                 reads the residual itself, in its own dtype)
 // which is what a layer of the form x <- x + m * norm_b(f(norm_a(x))) needs between f and the next f.  The variance
 // is the mean of the squared deviations from the mean (two passes over the row, which sits in registers or shared memory);
 // all sums are float32 in an order that depends on the row width only.  Embedding rows may be scaled on the way
@@ -60,7 +61,13 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const TA* __restrict
     } else {
         for (int i = threadIdx.x; i < E; i += blockDim.x) buf[i] = xr[i];
     }
-    if (!w) return;
+    if (!w) {
+        if (y) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < E; i += blockDim.x) y[(size_t)r * E + i] = from_float<TY>(buf[i]);
+        }
+        return;
+    }
     __syncthreads();
     float mean, inv;
     row_stats(buf, E, eps, scratch, mean, inv);
@@ -139,7 +146,18 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ x, const TA* __rest
 #pragma unroll
         for (int k = 0; k < ROUNDS; ++k) v[k] = xv[k];
     }
-    if (!w) return;
+    if (!w) {
+        if (y) {
+#pragma unroll
+            for (int k = 0; k < ROUNDS; ++k) {
+                const int i = (threadIdx.x + k * blockDim.x) * 4;
+                if (i >= E) continue;
+                const float o[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+                store4(y + (size_t)r * E + i, o);
+            }
+        }
+        return;
+    }
     float mean, inv;
     stats(eps, mean, inv);
     TY* yr = y + (size_t)r * E;

@@ -3,7 +3,10 @@
 //
 //   route          per token: the router's logits w x + b in float32 (the router's matrix is float32 whatever the
 //                  model's dtype), the `top` largest of them (the lower index wins a tie), and the softmax over the
-//                  chosen logits alone.
+//                  chosen logits alone (scoring 0).  Scoring 1: scores s = sigmoid(logit); the choice goes by s + correction
+//                  (a vector per expert), the weights are the chosen experts' s as they are; with groups > 1 the experts
+//                  form `groups` equal runs of neighbours, a run's rank is the sum of its two largest choice values, and
+//                  only experts of the `keep` best runs (the lower index on a tie) can be chosen.
 //   route_sort     the (token, choice) pairs sorted by expert: position of each pair, pair at each position, and a
 //                  list of row tiles (expert, first position, rows) that never cross from one expert to the next.
 //   gemm_grouped   y[i] = W[expert of i] x[source row of i] for the sorted positions i, tile by tile; float32
@@ -13,7 +16,8 @@
 //                  that feature's weight row once, 16 bytes per lane and load, for up to eight rows of the tile at a
 //                  time; a row's sum is taken in one order (lane by lane over k, then a butterfly), whatever else
 //                  the tile holds.  This is weight streaming: its bound is the bytes of the chosen experts.
-//   route_combine  out[t] = sum over the token's choices, in the order of the choices, weight * y[position of (t, j)].
+//   route_combine  out[t] = base[t] (optional: float32 partial sums of a part that runs for every token) + the sum over the
+//                  token's choices, in the order of the choices, of weight * y[position of (t, j)].
 #include "common.cuh"
 
 namespace {
@@ -32,10 +36,14 @@ constexpr int RT_WARPS = 16, MAX_EXPERTS = 1024;
 template <typename TX, int TOK>
 __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, int T, int E, int K, int top,
-                                                              int32_t* __restrict__ choice, float* __restrict__ weight) {
-    __shared__ float logit[TOK][MAX_EXPERTS / TOK];
+                                                              int32_t* __restrict__ choice, float* __restrict__ weight, int scoring,
+                                                              const float* __restrict__ correction, int groups, int keep) {
+    __shared__ float logit[TOK][MAX_EXPERTS / TOK];             // what the choice goes by
+    __shared__ float score[TOK][MAX_EXPERTS / TOK];             // scoring 1: sigmoid(logit), what the weights are
+    __shared__ float run_rank[TOK][MAX_EXPERTS / TOK];
     __shared__ unsigned char taken[TOK][MAX_EXPERTS / TOK];
     __shared__ float picked_value[TOK][MAX_TOP];
+    __shared__ int picked_index[TOK][MAX_TOP];
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -74,12 +82,45 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
 #pragma unroll
         for (int i = 0; i < TOK; ++i) {
             const float total = warp_sum(acc[i]);
-            if (lane == 0) { logit[i][e] = total + (bias ? bias[e] : 0.0f); taken[i][e] = 0; }
+            if (lane == 0) {
+                float z = total + (bias ? bias[e] : 0.0f);
+                if (scoring == 1) {
+                    z = 1.0f / (1.0f + expf(-z));
+                    score[i][e] = z;
+                    if (correction) z += correction[e];
+                }
+                logit[i][e] = z;
+                taken[i][e] = 0;
+            }
         }
     }
     __syncthreads();
     if (warp >= TOK || t0 + warp >= T) return;                 // one warp per token picks
     const int t = t0 + warp;
+    if (groups > 1 && keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float first = -INFINITY, second = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = logit[warp][e];
+                if (v > first) { second = first; first = v; }
+                else if (v > second) second = v;
+            }
+            run_rank[warp][g] = per > 1 ? first + second : first;
+        }
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) {
+            const float mine = run_rank[warp][g];
+            int ahead = 0;
+            for (int o = 0; o < groups; ++o) {
+                const float other = run_rank[warp][o];
+                ahead += (other > mine || (other == mine && o < g)) ? 1 : 0;
+            }
+            if (ahead >= keep)
+                for (int e = g * per; e < (g + 1) * per; ++e) taken[warp][e] = 1;
+        }
+        __syncwarp();
+    }
     for (int j = 0; j < top; ++j) {
         int best = -1;
         float best_v = 0.0f;
@@ -97,9 +138,14 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
         if (lane == 0) {
             taken[warp][best] = 1;
             picked_value[warp][j] = best_v;
+            picked_index[warp][j] = best;
             choice[(size_t)t * top + j] = best;
         }
         __syncwarp();
+    }
+    if (scoring == 1) {
+        if (lane < top) weight[(size_t)t * top + lane] = score[warp][picked_index[warp][lane]];
+        return;
     }
     const float largest = picked_value[warp][0];
     const float mine = lane < top ? expf(picked_value[warp][lane] - largest) : 0.0f;
@@ -296,13 +342,16 @@ __global__ void route_gather_vec_kernel(const TX* __restrict__ x, const int32_t*
 
 template <typename TY>
 __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
-                                     int top, float* __restrict__ out, int E_out, long long total) {
+                                     int top, float* __restrict__ out, int E_out, long long total, const float* __restrict__ base,
+                                     int base_splits, long long base_stride) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int t = (int)(idx / E_out), c = (int)(idx % E_out);
     float acc = 0.0f;
+    if (base)
+        for (int s = 0; s < base_splits; ++s) acc += base[(size_t)s * base_stride + idx];
     for (int j = 0; j < top; ++j)
         acc += weight[(size_t)t * top + j] * to_float<TY>(y[(size_t)position[(size_t)t * top + j] * E_out + c]);
     out[idx] = acc;
@@ -310,7 +359,8 @@ __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __
 
 // float32 y, four columns per thread
 __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
-                                         int top, float* __restrict__ out, int E_out, long long total4) {
+                                         int top, float* __restrict__ out, int E_out, long long total4, const float* __restrict__ base,
+                                         int base_splits, long long base_stride) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -318,6 +368,11 @@ __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int3
     const int per_row = E_out / 4;
     const int t = (int)(idx / per_row), c = (int)(idx % per_row) * 4;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (base)
+        for (int s = 0; s < base_splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(base + (size_t)s * base_stride + (size_t)t * E_out + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
     for (int j = 0; j < top; ++j) {
         const float wj = weight[(size_t)t * top + j];
         const float4 v = *reinterpret_cast<const float4*>(y + (size_t)position[(size_t)t * top + j] * E_out + c);
@@ -329,10 +384,15 @@ __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int3
 }  // namespace
 
 // x [T, K] (the model's dtype), w [E, K] float32, bias [E] or null -> choice [T, top], weight [T, top].
+// scoring 0: softmax over the chosen logits; 1: sigmoid scores, the choice by score + correction (null: none), within the
+// `keep` best of `groups` runs of neighbouring experts (groups 1: no runs).
 PH_EXPORT int ph_route(const void* x, int x_dtype, const float* w, const float* bias, int T, int E, int K, int top, int32_t* choice,
-                       float* weight, cudaStream_t stream) {
+                       float* weight, int scoring, const float* correction, int groups, int keep, cudaStream_t stream) {
     if (!x || !w || !choice || !weight || T < 0 || E < 1 || K < 1 || top < 1 || top > E || !valid_dtype(x_dtype))
         return fail(PH_ERR_ARG, "route: bad arguments (T %d, experts %d, K %d, top %d)", T, E, K, top);
+    if (scoring < 0 || scoring > 1 || groups < 1 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
+        return fail(PH_ERR_ARG, "route: scoring %d with %d of %d runs of %d experts cannot give %d choices", scoring, keep, groups,
+                    E / (groups > 0 ? groups : 1), top);
     if (top > MAX_TOP || E > MAX_EXPERTS)
         return fail(PH_ERR_UNSUPPORTED, "route: top %d of %d experts exceeds the supported %d of %d", top, E, MAX_TOP, MAX_EXPERTS);
     if (T == 0) return PH_OK;
@@ -340,10 +400,10 @@ PH_EXPORT int ph_route(const void* x, int x_dtype, const float* w, const float* 
     if (!aligned) return fail(PH_ERR_ARG, "route: the rows must be 16-byte aligned");
     if (T >= 64 && E <= MAX_EXPERTS / 4)
         PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 4>, dim3((T + 3) / 4), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w,
-                                                   bias, T, E, K, top, choice, weight));
+                                                   bias, T, E, K, top, choice, weight, scoring, correction, groups, keep));
     else
         PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 1>, dim3(T), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w, bias, T,
-                                                   E, K, top, choice, weight));
+                                                   E, K, top, choice, weight, scoring, correction, groups, keep));
     return check_launch("route");
 }
 
@@ -415,17 +475,17 @@ PH_EXPORT int ph_gemv_grouped(const void* x, int x_dtype, const int32_t* pair_at
 }
 
 PH_EXPORT int ph_route_combine(const void* y, int y_dtype, const int32_t* position, const float* weight, int T, int top, int E_out,
-                               float* out, cudaStream_t stream) {
-    if (!y || !position || !weight || !out || T < 0 || top < 1 || E_out < 1 || !valid_dtype(y_dtype))
+                               float* out, const float* base, int base_splits, long long base_stride, cudaStream_t stream) {
+    if (!y || !position || !weight || !out || T < 0 || top < 1 || E_out < 1 || !valid_dtype(y_dtype) || (base && base_splits < 1))
         return fail(PH_ERR_ARG, "route_combine: bad arguments (T %d, top %d, width %d)", T, top, E_out);
     const long long total = (long long)T * E_out;
     if (total == 0) return PH_OK;
-    if (y_dtype == PH_F32 && E_out % 4 == 0 && (((uintptr_t)y | (uintptr_t)out) & 15) == 0) {
+    if (y_dtype == PH_F32 && E_out % 4 == 0 && (((uintptr_t)y | (uintptr_t)out | (uintptr_t)base) & 15) == 0 && base_stride % 4 == 0) {
         launch_overlapped(route_combine_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (const float*)y, position,
-                          weight, top, out, E_out, total / 4);
+                          weight, top, out, E_out, total / 4, base, base_splits, base_stride);
         return check_launch("route_combine");
     }
     PH_DISPATCH(y_dtype, TY, launch_overlapped(route_combine_kernel<TY>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                                               (const TY*)y, position, weight, top, out, E_out, total));
+                                               (const TY*)y, position, weight, top, out, E_out, total, base, base_splits, base_stride));
     return check_launch("route_combine");
 }

@@ -159,6 +159,9 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_add_layernorm", g_core.add_layernorm);
     bind(h, "core", "ph_embed_gather_scaled", g_core.embed_gather_scaled);
     bind(h, "core", "ph_glu", g_core.glu);
+    bind(h, "core", "ph_unary_act", g_core.unary_act);
+    bind(h, "core", "ph_decayed_scan", g_core.decayed_scan);
+    bind(h, "core", "ph_rms_pair_mean", g_core.rms_pair_mean);
     bind(h, "core", "ph_causal_conv_silu", g_core.causal_conv_silu);
     bind(h, "core", "ph_selective_scan", g_core.selective_scan);
     bind(h, "core", "ph_route", g_core.route);

@@ -99,7 +99,7 @@ struct CoreKernels {
                                  const float*, int, cudaStream_t);
     int (*add_weight_sumsq)(float*, const void*, int, int, long long, const float*, int, int, void*, int, float*, int, cudaStream_t);
     int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
-                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, cudaStream_t);
+                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, int, cudaStream_t);
     int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
     int (*argmax)(const float*, int, int, int32_t*, void*, long long, cudaStream_t);   // several CTAs per row, with scratch
     long long (*argmax_scratch_bytes)(int);
@@ -113,14 +113,25 @@ struct CoreKernels {
     int (*embed_gather_scaled)(const void*, int, const int32_t*, float*, int, int, int, float, cudaStream_t);
     // gated activations by kind (0 silu, 1 clamped swish with alpha, limit, shift)
     int (*glu)(const void*, int, int, long long, void*, int, int, int, int, float, float, float, cudaStream_t);
+    // activations of one argument over plain rows (0 silu, 1 the square of relu)
+    int (*unary_act)(const void*, int, int, long long, void*, int, long long, int, cudaStream_t);
+    // gated linear attention: the decayed matrix state token by token with the head norm and gate behind it; two mixers'
+    // outputs, each RMS-normed over the width, combined
+    int (*decayed_scan)(const void*, const void*, const void*, const void*, int, long long, const float*, long long, const float*, float,
+                        float, const float*, float, float*, long long, const int32_t*, const int32_t*, int, int, int, int, int, float*,
+                        void*, cudaStream_t);
+    int (*rms_pair_mean)(const void*, int, int, long long, const float*, const void*, int, int, long long, const float*, float, float,
+                         float*, int, int, cudaStream_t);
     // selective state-space mixer: convolution + silu, and the scan
     int (*causal_conv_silu)(const void*, int, long long, int, const float*, const float*, int, const float*, long long, long long,
                             const int32_t*, const int32_t*, const int32_t*, void*, int, int, cudaStream_t);
     int (*selective_scan)(const void*, const float*, const float*, const void*, long long, int, int, int, const float*,
                           const float*, const void*, long long, int, int, float*, long long, const int32_t*, const int32_t*, int,
                           const int32_t*, int, const int32_t*, float*, float*, void*, int, cudaStream_t);
-    // routing: router logits and top-k with softmax over the chosen, sort by expert, products by expert, weighted sum
-    int (*route)(const void*, int, const float*, const float*, int, int, int, int, int32_t*, float*, cudaStream_t);
+    // routing: router logits and top-k (softmax over the chosen, or sigmoid scores with a correction and runs of experts),
+    // sort by expert, products by expert, weighted sum (on top of a base addend)
+    int (*route)(const void*, int, const float*, const float*, int, int, int, int, int32_t*, float*, int, const float*, int, int,
+                 cudaStream_t);
     int (*route_max_tiles)(int, int);
     int (*route_sort)(const int32_t*, int, int, int32_t*, int32_t*, int32_t*, int, int32_t*, cudaStream_t);
     int (*gemm_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
@@ -128,7 +139,7 @@ struct CoreKernels {
     int (*gemv_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
                         cudaStream_t);
     int (*route_gather)(const void*, int, const int32_t*, int, void*, int, int, cudaStream_t);
-    int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, cudaStream_t);
+    int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, const float*, int, long long, cudaStream_t);
     const char* (*last_error)(void);
 };
 struct FlashKernels {

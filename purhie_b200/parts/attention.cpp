@@ -3,7 +3,8 @@
 // q = Wq x, k = Wk x, v = Wv x (+ optional biases, added before the norms); each q and k head is RMS-normalised
 // over head_dim with a weight shared by all heads (same eps as the layer norms), then rotated; k and v go into
 // the request's pages; query head h attends with kv head h / (HQ / HKV), scale 1 / sqrt(head_dim), causally,
-// optionally only over the last `window` positions; then y = Wo o.
+// optionally only over the last `window` positions, or only over the positions of its own block of `chunk` positions
+// (blocks counted from position 0 of the request, wherever a prompt was cut); then y = Wo o.
 // Reference: src/qwen_model.cpp:940-975 (full_attention), src/attention.hip:273-313 (prep),
 // src/attention.cpp:139-288 (host side; scale at :197), src/attention.h:73 (window),
 // src/inference.cpp:623-646 (tensors and shapes).
@@ -110,8 +111,8 @@ void add_tiles(StepPlan& plan, int rows, const std::string& name) {
 }  // namespace
 
 // params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim (null: head_dim), qk_norm_eps (null: no q/k norm),
-// bias, position (a PartSpec as {kind, params}, or null), window (null: all positions), scale (null:
-// 1/sqrt(head_dim)), value_mix (null | "first" | "blend"),
+// bias, position (a PartSpec as {kind, params}, or null), window (null: all positions), chunk (null: no block mask),
+// scale (null: 1/sqrt(head_dim)), value_mix (null | "first" | "blend"),
 // names{q_proj, k_proj, v_proj, o_proj, q_norm, k_norm, q_bias, k_bias, v_bias, value_mix_factor}.
 class Attention : public Mixer {
 public:
@@ -132,6 +133,8 @@ public:
         eps_ = has_norm_ ? eps->as_double() : 0.0;
         has_bias_ = p.get_bool("bias", false);
         window_ = (int)p.get_int("window", 0);
+        chunk_ = (int)p.get_int("chunk", 0);
+        if (chunk_ < 0) throw ConfigError("attention: a block mask holds at least one position");
         const Json* sc = p.find("scale");
         scale_ = (sc && !sc->is_null()) ? sc->as_double() : 1.0 / std::sqrt((double)head_dim_);
         if (const Json* pos = p.find("position")) {
@@ -226,6 +229,7 @@ public:
 
     bool use_flash() const {
         if (compute_dtype != DType::BF16 || attention_ == "generic") return false;
+        if (chunk_) return false;                 // the block mask is the plain kernel's
         const int group = heads_ / kv_heads_;
         const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16;
         if (!ok && attention_ == "flash")
@@ -235,7 +239,7 @@ public:
     }
 
     // ---- cache and step metadata ------------------------------------------------------------------------------
-    CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_); }
+    CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_, chunk_); }
 
     void prepare_step(StepPlan& plan) override {
         if (!use_flash()) return;
@@ -298,9 +302,10 @@ public:
             double seen = 0.0, read = 0.0;
             for (size_t i = 0; i < ctx.q_lens.size(); i++) {
                 const double n = ctx.q_lens[i], len = ctx.ctx_lens[i];
-                const double span = window_ ? std::min<double>(len, window_ + n) : len;
+                const int reach = chunk_ ? (window_ ? std::min(window_, chunk_) : chunk_) : window_;
+                const double span = reach ? std::min<double>(len, reach + n) : len;
                 read += span;
-                seen += window_ ? n * std::min<double>(len, window_) : n * (len - n) + n * (n + 1) / 2.0;
+                seen += reach ? n * std::min<double>(len, chunk_ ? reach / 2.0 : reach) : n * (len - n) + n * (n + 1) / 2.0;
             }
             const double kv = dtype_size(cache.kv_dtype);
             LaunchProfile::get().note_cost(read * kv_heads_ * (head_dim_ + value_dim_) * kv + (double)T * (q_width_ + o_width_) * dtype_size(dt),
@@ -312,7 +317,7 @@ public:
         } else {
             QE_LAUNCH(core, core.attention_generic(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                    cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
-                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_,
+                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_,
                                                    ctx.stream));
         }
         return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
@@ -368,7 +373,7 @@ private:
     }
 
     int64_t hidden_, q_width_, kv_width_, v_width_, o_width_;
-    int heads_, kv_heads_, head_dim_, value_dim_, window_, value_mix_ = 0;
+    int heads_, kv_heads_, head_dim_, value_dim_, window_, chunk_ = 0, value_mix_ = 0;
     bool has_norm_, has_bias_;
     double eps_, scale_;
     std::string gemm_, attention_;

@@ -106,6 +106,7 @@ private:
 void register_norm_parts();
 void register_routed_parts();
 void register_state_space_parts();
+void register_linear_attention_parts();
 void register_position_parts();
 void register_mixer_parts();
 void register_feed_forward_parts();
@@ -122,6 +123,7 @@ void register_builtin_parts() {
     register_embedding_parts();
     register_routed_parts();
     register_state_space_parts();
+    register_linear_attention_parts();
     register_arrangement("sandwich_norm", [](const LayerSpec& layer, BuildContext& build) {
         return std::unique_ptr<Arrangement>(new SandwichNormBlock(layer, build));
     });

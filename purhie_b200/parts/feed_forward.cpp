@@ -1,6 +1,8 @@
 // Gated feed-forward: y = Wd act(Wg x, Wu x), with act(g, u) = silu(g) * u (SwiGLU) unless the part is given another
 // gate: "clamped_swish" is g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
 //
+// A feed-forward without a gate ("mlp") is y = Wd act(Wu x).
+//
 // Reference: src/qwen_model.cpp:1170-1189 (gate and up as one grouped product, the activation, down),
 // src/gpu_ops.hip:103-114 (silu(g) * u with g / (1 + exp(-g))).
 #include "gate.h"
@@ -79,7 +81,44 @@ private:
     Linear gate_up_, down_;
 };
 
+// A feed-forward without a gate: y = Wd act(Wu x), act of one argument ("relu2": the square of relu; "silu").
+// params: hidden_size, intermediate_size, activation, names{up_proj, down_proj}.
+class PlainMLP : public FeedForward {
+public:
+    PlainMLP(const Json& p, BuildContext& b)
+        : FeedForward(p, b), hidden_(p.at("hidden_size").as_int()), inter_(p.at("intermediate_size").as_int()),
+          gemm_(b.options.get_string("gemm", "auto")), act_(unary_activation(p.get_string("activation", "silu"))) {}
+
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("up_proj"), {inter_, hidden_}, Role::Matrix, Init::Normal}, {name_of("down_proj"), {hidden_, inter_}, Role::Matrix, Init::Normal}};
+    }
+    void bind(WeightSource& src) override {
+        up_ = Linear(src.fetch(name_of("up_proj")), "up_proj", gemm_);
+        down_ = Linear(src.fetch(name_of("down_proj")), "down_proj", gemm_);
+    }
+    std::vector<std::string> required_libraries() const override {
+        return (up_.fast() || down_.fast()) ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
+    }
+    Addend forward(const Tensor& x, StepContext& ctx) override {
+        const int T = ctx.T;
+        Addend u = up_(x, ctx, "mlp_up", compute_dtype, T, true);
+        Tensor act = ctx.workspace->get("mlp_act", {T, inter_}, compute_dtype);
+        const CoreKernels& k = core_kernels();
+        if (LaunchProfile::get().on())
+            LaunchProfile::get().note_cost((double)T * inter_ * (u.splits * dtype_size(u.tensor.dtype) + dtype_size(compute_dtype)), 0.0);
+        QE_LAUNCH(k, k.unary_act(u.tensor.data, u.tensor.code(), u.splits, (long long)T * inter_, act.data, act.code(), (long long)T * inter_,
+                                 act_, ctx.stream));
+        return down_(act, ctx, "mlp_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
+    }
+private:
+    int64_t hidden_, inter_;
+    std::string gemm_;
+    int act_;
+    Linear up_, down_;
+};
+
 void register_feed_forward_parts() {
+    register_part("feed_forward", "mlp", [](const Json& p, BuildContext& b) { return std::make_shared<PlainMLP>(p, b); });
     register_part("feed_forward", "swiglu", [](const Json& p, BuildContext& b) { return std::make_shared<SwiGLU>(p, b); });
 }
 

@@ -28,4 +28,11 @@ struct GateSpec {
     }
 };
 
+// An activation of one argument, for a feed-forward without a gate: "silu" (0), "relu2" (1: the square of relu).
+inline int unary_activation(const std::string& name) {
+    if (name == "silu") return 0;
+    if (name == "relu2") return 1;
+    throw ConfigError("feed-forward: activation '" + name + "' is not known (silu, relu2)");
+}
+
 }  // namespace qe

@@ -1,4 +1,5 @@
-// The norms: RMSNorm and the layer norm with weight and bias, each with the residual add folded in.
+// The norms: RMSNorm, the layer norm with weight and (optional) bias, and "none" for a part that reads the residual
+// itself, each with the residual add folded in.
 //
 // y = v * rsqrt(mean(v^2) + eps) * w, v = x + pending addend; the weight multiplies after normalising (plain w,
 // not 1 + w).  Reference: src/gpu_ops.hip:24-56 (add + norm in one kernel), src/qwen_ops.cpp:8-13.
@@ -101,18 +102,21 @@ private:
 // deviations, v = x + the pending addend.  A pending addend may carry a transform (a norm of this kind over the
 // addend's own rows and a factor): the one kernel applies it, adds, and norms the sum, which is all a layer of the
 // form x <- x + m * norm_b(f(norm_a(x))) needs between two parts.
-// params: size, eps, names{weight, bias}.
+// params: size, eps, names{weight, bias}; without a name for the bias the norm has none.
 class LayerNorm : public Norm {
 public:
     LayerNorm(const Json& p, BuildContext& b) : Norm(p, b), size_(p.at("size").as_int()), eps_(p.at("eps").as_double()) {
         if (size_ < 1 || !(eps_ >= 0)) throw ConfigError("layernorm: size must be positive and eps >= 0");
+        has_bias_ = names_.count("bias") != 0;
     }
     std::vector<TensorSpec> tensor_specs() const override {
-        return {{name_of("weight"), {size_}, Role::Vector, Init::Scale}, {name_of("bias"), {size_}, Role::Vector, Init::Normal}};
+        std::vector<TensorSpec> s = {{name_of("weight"), {size_}, Role::Vector, Init::Scale}};
+        if (has_bias_) s.push_back({name_of("bias"), {size_}, Role::Vector, Init::Normal});
+        return s;
     }
     void bind(WeightSource& src) override {
         weight_ = src.fetch(name_of("weight"));
-        bias_ = src.fetch(name_of("bias"));
+        if (has_bias_) bias_ = src.fetch(name_of("bias"));
     }
     Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
         const int n = rows ? n_rows : ctx.T;
@@ -123,25 +127,52 @@ public:
         QE_LAUNCH(k, k.add_layernorm(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
                                      a ? (long long)ctx.T * size_ : 0, a ? a->transform.weight : nullptr, a ? a->transform.bias : nullptr,
                                      a ? a->transform.eps : 0.0f, a ? a->transform.factor : 1.0f, weight_.as<float>(),
-                                     bias_.as<float>(), (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1,
-                                     ctx.stream));
+                                     has_bias_ ? bias_.as<float>() : nullptr, (float)eps_, rows, n, (int)size_, out.data, out.code(),
+                                     rows ? 0 : 1, ctx.stream));
         if (!rows) stream.clear();
         return out;
     }
     AddendTransform as_transform(float factor) const override {
         AddendTransform t;
-        t.weight = weight_.as<float>(); t.bias = bias_.as<float>(); t.eps = (float)eps_; t.factor = factor;
+        t.weight = weight_.as<float>(); t.bias = has_bias_ ? bias_.as<float>() : nullptr; t.eps = (float)eps_; t.factor = factor;
         return t;
     }
 private:
     int64_t size_;
     double eps_;
+    bool has_bias_ = true;
     Tensor weight_, bias_;
+};
+
+// No norm at all, for a layer whose parts read the residual stream as it is (and norm what they give instead): the
+// pending addend, with its transform, is folded in, and the rows come back in the compute dtype, in the same one pass.
+// params: size.
+class NoNorm : public Norm {
+public:
+    NoNorm(const Json& p, BuildContext& b) : Norm(p, b), size_(p.at("size").as_int()) {
+        if (size_ < 1) throw ConfigError("norm 'none': size must be positive");
+    }
+    Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
+        const int n = rows ? n_rows : ctx.T;
+        Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
+        const CoreKernels& k = core_kernels();
+        const Addend* a = stream.has_pending ? &stream.pending : nullptr;
+        note_norm_cost(stream, n, size_, compute_dtype, !rows);
+        QE_LAUNCH(k, k.add_layernorm(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
+                                     a ? (long long)ctx.T * size_ : 0, a ? a->transform.weight : nullptr, a ? a->transform.bias : nullptr,
+                                     a ? a->transform.eps : 0.0f, a ? a->transform.factor : 1.0f, nullptr, nullptr, 0.0f, rows, n,
+                                     (int)size_, out.data, out.code(), rows ? 0 : 1, ctx.stream));
+        if (!rows) stream.clear();
+        return out;
+    }
+private:
+    int64_t size_;
 };
 
 void register_norm_parts() {
     register_part("norm", "rmsnorm", [](const Json& p, BuildContext& b) { return std::make_shared<RMSNorm>(p, b); });
     register_part("norm", "layernorm", [](const Json& p, BuildContext& b) { return std::make_shared<LayerNorm>(p, b); });
+    register_part("norm", "none", [](const Json& p, BuildContext& b) { return std::make_shared<NoNorm>(p, b); });
 }
 
 }  // namespace qe

@@ -47,7 +47,7 @@ enum class Init { Normal, Scale };              // random weights: N(0, std) | U
 
 struct TensorSpec {
     std::string name;
-    std::vector<int64_t> shape;
+    std::vector<int64_t> shape;                 // a dimension of -1: as stored (a size that no configuration key gives); the part reads it when it binds
     Role role = Role::Matrix;
     Init init = Init::Normal;
     bool operator==(const TensorSpec& o) const { return name == o.name && shape == o.shape && role == o.role && init == o.init; }
@@ -73,18 +73,33 @@ struct CacheNeed {
     int kv_heads = 0, head_dim = 0;
     int value_dim = 0;                            // pages: width of a value row when it differs from a key row's (0: head_dim)
     int window = 0;                               // pages: 0 keeps all keys, W keeps the last W positions
+    int chunk = 0;                                // pages: C > 0 keeps the keys of the block of C positions (counted from 0) that the next position is in
     int v_dim() const { return value_dim > 0 ? value_dim : head_dim; }
-    std::vector<int64_t> state_shape;             // state: shape of one request's state
+    std::vector<int64_t> state_shape;             // state: shape of one request's state (a mixer of pages may keep one too)
     DType state_dtype = DType::F32;
-    static CacheNeed pages(int kv_heads, int head_dim, int window = 0, int value_dim = 0) {
+    bool has_state() const { return !state_shape.empty(); }
+    static CacheNeed pages(int kv_heads, int head_dim, int window = 0, int value_dim = 0, int chunk = 0) {
         if (window < 0) throw Error(kInvalidArg, "a window must hold at least one position");
+        if (chunk < 0) throw Error(kInvalidArg, "a block of positions must hold at least one position");
         if (kv_heads < 1 || head_dim < 1 || value_dim < 0) throw Error(kInvalidArg, "a page holds at least one head of at least one element");
-        CacheNeed n; n.kind = Pages; n.kv_heads = kv_heads; n.head_dim = head_dim; n.window = window;
+        CacheNeed n; n.kind = Pages; n.kv_heads = kv_heads; n.head_dim = head_dim; n.window = window; n.chunk = chunk;
         n.value_dim = value_dim == head_dim ? 0 : value_dim;
         return n;
     }
     static CacheNeed state(std::vector<int64_t> shape, DType dtype = DType::F32) {
         CacheNeed n; n.kind = State; n.state_shape = std::move(shape); n.state_dtype = dtype; return n;
+    }
+    // What two mixers that run side by side in one layer need together: the pages of the one and the state of the other
+    // (one of each at most).
+    static CacheNeed both(const CacheNeed& a, const CacheNeed& b) {
+        if (a.kind == None) return b;
+        if (b.kind == None) return a;
+        if ((a.kind == Pages && b.kind == Pages) || (a.has_state() && b.has_state()))
+            throw Error(kInvalidArg, "two mixers of one layer cannot both keep pages, or both keep state");
+        CacheNeed n = a.kind == Pages ? a : b;
+        const CacheNeed& other = a.kind == Pages ? b : a;
+        n.state_shape = other.state_shape; n.state_dtype = other.state_dtype;
+        return n;
     }
 };
 
@@ -143,7 +158,7 @@ struct CacheView {
     int page_size = 0;
     int num_pages = 0;
     bool writable = true;                    // false: another entry writes this cache, this one only reads
-    Tensor state;                            // [max_requests, *state_shape]
+    Tensor state;                            // [max_requests, *state_shape]; defined whenever the entry keeps state (beside pages too)
 };
 
 // What is done to each row of an addend on its way into the residual: a layer norm over the row with weight and bias

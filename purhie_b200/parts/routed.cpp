@@ -5,6 +5,12 @@
 // index on a tie) with weights softmax(z over the chosen).  An expert is the gated unit of feed_forward.cpp without
 // biases; the token's output is the weighted sum of its experts' outputs, added in the order of the choices.
 //
+// Other designs' options: "scoring": {"kind": "sigmoid", "groups", "keep"}: scores s = sigmoid(z); the choice goes by
+// s + correction (a vector per expert, names.correction; without it by s), restricted to the `keep` runs of neighbouring
+// experts (of `groups` equal runs) whose two largest choice values add up highest; the weights are the chosen
+// experts' s as they are.  "gated": false: an expert is Wd act(Wu x) with an activation of one argument ("relu2").
+// "shared": {kind, params}: a feed-forward that runs for every token and is added to the chosen experts' sum.
+//
 // The (token, choice) pairs are sorted by expert on the device.  Which kernels then multiply:
 //   * few pairs (decoding): one launch per matrix of a kernel that streams each chosen expert's weight rows once
 //     (gemv_grouped); no count reaches the host, so the step is captured as a graph like any other;
@@ -23,27 +29,50 @@
 
 namespace qe {
 
-// params: hidden_size, intermediate_size, experts, top, activation (as the gated feed-forward's), names{router,
-// router_bias (optional)}, expert_names [{gate_proj, up_proj, down_proj} per expert].
+// params: hidden_size, intermediate_size, experts, top, gated (default true), activation (as the gated feed-forward's;
+// without a gate a name as the plain feed-forward's), scoring (null or as above), shared (null or {kind, params}),
+// names{router, router_bias (optional), correction (optional)}, expert_names [{gate_proj, up_proj, down_proj} per
+// expert; without a gate {up_proj, down_proj}].
 class RoutedGLU : public FeedForward {
 public:
     RoutedGLU(const Json& p, BuildContext& b)
         : FeedForward(p, b), hidden_(p.at("hidden_size").as_int()), inter_(p.at("intermediate_size").as_int()),
-          experts_((int)p.at("experts").as_int()), top_((int)p.at("top").as_int()), gate_(GateSpec::read(p)) {
+          experts_((int)p.at("experts").as_int()), top_((int)p.at("top").as_int()) {
         if (experts_ < 1 || top_ < 1 || top_ > experts_)
             throw ConfigError("routed feed-forward: top " + std::to_string(top_) + " of " + std::to_string(experts_) + " experts");
+        gated_ = p.get_bool("gated", true);
+        if (gated_) gate_ = GateSpec::read(p);
+        else unary_ = unary_activation(p.get_string("activation", "silu"));
+        up_width_ = gated_ ? 2 * inter_ : inter_;
         const Json& names = p.at("expert_names");
         if (!names.is_array() || (int)names.size() != experts_) throw ConfigError("routed feed-forward: expert_names must list every expert");
         for (const Json& n : names.items())
-            expert_names_.push_back({n.at("gate_proj").as_string(), n.at("up_proj").as_string(), n.at("down_proj").as_string()});
+            expert_names_.push_back({gated_ ? n.at("gate_proj").as_string() : std::string(), n.at("up_proj").as_string(), n.at("down_proj").as_string()});
         has_bias_ = names_.count("router_bias") != 0;
+        has_correction_ = names_.count("correction") != 0;
+        if (const Json* sc = p.find("scoring")) {
+            if (!sc->is_null()) {
+                const std::string kind = sc->get_string("kind", "");
+                if (kind != "sigmoid") throw ConfigError("routed feed-forward: scoring of kind '" + kind + "' is not known (sigmoid is)");
+                scoring_ = 1;
+                groups_ = (int)sc->get_int("groups", 1);
+                keep_ = (int)sc->get_int("keep", groups_);
+                if (groups_ < 1 || experts_ % groups_ || keep_ < 1 || keep_ > groups_ || (long long)keep_ * (experts_ / groups_) < top_)
+                    throw ConfigError("routed feed-forward: " + std::to_string(keep_) + " of " + std::to_string(groups_) + " runs of " +
+                                      std::to_string(experts_) + " experts cannot give " + std::to_string(top_) + " choices");
+            }
+        }
+        if (has_correction_ && !scoring_) throw ConfigError("routed feed-forward: a correction of the choice needs sigmoid scoring");
+        if (const Json* sh = p.find("shared"))
+            if (!sh->is_null()) shared_ = make_part_as<FeedForward>("feed_forward", PartSpec::from_json(*sh), b);
     }
 
     std::vector<TensorSpec> tensor_specs() const override {
         std::vector<TensorSpec> s = {{name_of("router"), {experts_, hidden_}, Role::Vector, Init::Normal}};
         if (has_bias_) s.push_back({name_of("router_bias"), {experts_}, Role::Vector, Init::Normal});
+        if (has_correction_) s.push_back({name_of("correction"), {experts_}, Role::Vector, Init::Normal});
         for (const auto& n : expert_names_) {
-            s.push_back({n[0], {inter_, hidden_}, Role::Matrix, Init::Normal});
+            if (gated_) s.push_back({n[0], {inter_, hidden_}, Role::Matrix, Init::Normal});
             s.push_back({n[1], {inter_, hidden_}, Role::Matrix, Init::Normal});
             s.push_back({n[2], {hidden_, inter_}, Role::Matrix, Init::Normal});
         }
@@ -53,32 +82,39 @@ public:
     void bind(WeightSource& src) override {
         router_ = src.fetch(name_of("router"));
         if (has_bias_) router_bias_ = src.fetch(name_of("router_bias"));
+        if (has_correction_) correction_ = src.fetch(name_of("correction"));
+        if (shared_) shared_->bind(src);
         // the experts' matrices stacked: [experts, 2 ff, hidden] with gate and up rows interleaved (g0, u0, g1, u1, ...)
-        // as the gated feed-forward lays them out, and [experts, hidden, ff]
+        // as the gated feed-forward lays them out (without a gate [experts, ff, hidden]), and [experts, hidden, ff]
         for (int e = 0; e < experts_; e++) {
-            Tensor gate = src.fetch(expert_names_[e][0]), up = src.fetch(expert_names_[e][1]), down = src.fetch(expert_names_[e][2]);
+            Tensor up = src.fetch(expert_names_[e][1]), down = src.fetch(expert_names_[e][2]);
+            Tensor gate = gated_ ? src.fetch(expert_names_[e][0]) : up;
             if (e == 0) {
-                gate_up_ = src.arena().alloc(gate.dtype, {experts_, 2 * inter_, hidden_});
+                gate_up_ = src.arena().alloc(up.dtype, {experts_, up_width_, hidden_});
                 down_ = src.arena().alloc(down.dtype, {experts_, hidden_, inter_});
             }
             if (gate.dtype != gate_up_.dtype || up.dtype != gate_up_.dtype || down.dtype != down_.dtype)
                 throw WeightError("the experts of a routed feed-forward are stored in different precisions");
-            const size_t row = (size_t)hidden_ * dtype_size(gate.dtype);
-            char* gu = static_cast<char*>(gate_up_.data) + (size_t)e * 2 * inter_ * row;
-            QE_CUDA(cudaMemcpy2DAsync(gu, 2 * row, gate.data, row, row, (size_t)inter_, cudaMemcpyDeviceToDevice, src.stream()));
-            QE_CUDA(cudaMemcpy2DAsync(gu + row, 2 * row, up.data, row, row, (size_t)inter_, cudaMemcpyDeviceToDevice, src.stream()));
+            const size_t row = (size_t)hidden_ * dtype_size(up.dtype);
+            char* gu = static_cast<char*>(gate_up_.data) + (size_t)e * up_width_ * row;
+            if (gated_) {
+                QE_CUDA(cudaMemcpy2DAsync(gu, 2 * row, gate.data, row, row, (size_t)inter_, cudaMemcpyDeviceToDevice, src.stream()));
+                QE_CUDA(cudaMemcpy2DAsync(gu + row, 2 * row, up.data, row, row, (size_t)inter_, cudaMemcpyDeviceToDevice, src.stream()));
+            } else {
+                QE_CUDA(cudaMemcpyAsync(gu, up.data, up.bytes(), cudaMemcpyDeviceToDevice, src.stream()));
+            }
             QE_CUDA(cudaMemcpyAsync(static_cast<char*>(down_.data) + (size_t)e * down.bytes(), down.data, down.bytes(),
                                     cudaMemcpyDeviceToDevice, src.stream()));
             QE_CUDA(cudaStreamSynchronize(src.stream()));
-            src.release(gate);
+            if (gated_) src.release(gate);
             src.release(up);
             src.release(down);
         }
         // each expert's two matrices as products of their own, for the steps that run them slice by slice
         const std::string gemm = compute_dtype == DType::BF16 ? "auto" : "simple";
         for (int e = 0; e < experts_; e++) {
-            Tensor gu(static_cast<char*>(gate_up_.data) + (size_t)e * 2 * inter_ * hidden_ * dtype_size(gate_up_.dtype), gate_up_.dtype,
-                      {2 * inter_, hidden_});
+            Tensor gu(static_cast<char*>(gate_up_.data) + (size_t)e * up_width_ * hidden_ * dtype_size(gate_up_.dtype), gate_up_.dtype,
+                      {up_width_, hidden_});
             Tensor dn(static_cast<char*>(down_.data) + (size_t)e * hidden_ * inter_ * dtype_size(down_.dtype), down_.dtype, {hidden_, inter_});
             expert_gate_up_.emplace_back(gu, "expert_gate_up", gemm);
             expert_down_.emplace_back(dn, "expert_down", gemm);
@@ -87,9 +123,14 @@ public:
     }
 
     std::vector<std::string> required_libraries() const override {
-        return (!expert_gate_up_.empty() && expert_gate_up_[0].fast()) ? std::vector<std::string>{"core", "gemm100"}
-                                                                         : std::vector<std::string>{"core"};
+        std::vector<std::string> libs = {"core"};
+        if (!expert_gate_up_.empty() && expert_gate_up_[0].fast()) libs.push_back("gemm100");
+        if (shared_)
+            for (const std::string& l : shared_->required_libraries()) libs.push_back(l);
+        return libs;
     }
+    std::vector<Part*> children() override { return shared_ ? std::vector<Part*>{shared_.get()} : std::vector<Part*>{}; }
+    void prepare_step(StepPlan& plan) override { if (shared_) shared_->prepare_step(plan); }
 
     Addend forward(const Tensor& x, StepContext& ctx) override {
         const int T = ctx.T, R = T * top_;
@@ -98,14 +139,29 @@ public:
         Tensor choice = ws.get("moe_choice", {T, top_}, DType::I32), weight = ws.get("moe_weight", {T, top_}, DType::F32);
         if (LaunchProfile::get().on())
             LaunchProfile::get().note_cost((double)T * hidden_ * dtype_size(x.dtype) + 4.0 * experts_ * hidden_, 2.0 * T * experts_ * hidden_);
+        // the part that runs for every token first: its result waits in the workspace (or is in the residual already)
+        Addend always;
+        if (shared_) {
+            // its sum joins the experts' below: it neither adds into the residual itself nor works ahead for a norm
+            float* residual = ctx.residual;
+            const NormAhead ahead = ctx.norm_ahead;
+            ctx.residual = nullptr;
+            ctx.norm_ahead = NormAhead();
+            always = shared_->forward(x, ctx);
+            ctx.residual = residual;
+            ctx.norm_ahead = ahead;
+            if (always.tensor.defined() && (always.tensor.dtype != DType::F32 || always.transform.defined()))
+                throw Error(kInvalidState, "routed feed-forward: the shared part must give float32 sums without a transform");
+        }
         QE_LAUNCH(k, k.route(x.data, x.code(), router_.as<float>(), router_bias_.defined() ? router_bias_.as<float>() : nullptr, T, experts_,
-                             (int)hidden_, top_, choice.as<int32_t>(), weight.as<float>(), ctx.stream));
+                             (int)hidden_, top_, choice.as<int32_t>(), weight.as<float>(), scoring_,
+                             correction_.defined() ? correction_.as<float>() : nullptr, groups_, keep_, ctx.stream));
         const int tiles = k.route_max_tiles(R, experts_);
         Tensor position = ws.get("moe_position", {R}, DType::I32), pair_at = ws.get("moe_pair_at", {R}, DType::I32);
         Tensor tile_list = ws.get("moe_tiles", {tiles, 3}, DType::I32), scratch = ws.get("moe_sort_scratch", {3 * experts_ + 1}, DType::I32);
         QE_LAUNCH(k, k.route_sort(choice.as<int32_t>(), R, experts_, position.as<int32_t>(), pair_at.as<int32_t>(),
                                   tile_list.as<int32_t>(), tiles, scratch.as<int32_t>(), ctx.stream));
-        Tensor gu = ws.get("moe_gate_up", {R, 2 * inter_}, compute_dtype);
+        Tensor gu = ws.get("moe_gate_up", {R, up_width_}, compute_dtype);
         Tensor act = ws.get("moe_act", {R, inter_}, compute_dtype);
         Tensor y = ws.get("moe_down", {R, hidden_}, DType::F32);
         const bool slices = !ctx.decode_only && R > kFewPairs && compute_dtype == DType::BF16 && x.dtype == DType::BF16 &&
@@ -139,11 +195,14 @@ public:
                 if (n > 0) expert_gate_up_[e].into(xs.rows(at, n), ctx, gu.rows(at, n), n);
             }
         } else {
-            grouped(x, pair_at.as<int32_t>(), top_, gate_up_, gu, 2 * inter_, hidden_);
+            grouped(x, pair_at.as<int32_t>(), top_, gate_up_, gu, up_width_, hidden_);
         }
-        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost(3.0 * R * inter_ * dtype_size(compute_dtype), 0.0);
-        QE_LAUNCH(k, k.glu(gu.data, gu.code(), 1, 0, act.data, act.code(), R, (int)inter_, gate_.kind, gate_.alpha, gate_.limit,
-                           gate_.shift, ctx.stream));
+        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost((double)R * (up_width_ + inter_) * dtype_size(compute_dtype), 0.0);
+        if (gated_)
+            QE_LAUNCH(k, k.glu(gu.data, gu.code(), 1, 0, act.data, act.code(), R, (int)inter_, gate_.kind, gate_.alpha, gate_.limit,
+                               gate_.shift, ctx.stream));
+        else
+            QE_LAUNCH(k, k.unary_act(gu.data, gu.code(), 1, 0, act.data, act.code(), (long long)R * inter_, unary_, ctx.stream));
         if (slices) {
             for (int e = 0; e < experts_; e++) {
                 const int at = first[e], n = first[e + 1] - first[e];
@@ -154,7 +213,8 @@ public:
         }
         Tensor out = ws.get("moe_out", {T, hidden_}, DType::F32);
         QE_LAUNCH(k, k.route_combine(y.data, y.code(), position.as<int32_t>(), weight.as<float>(), T, top_, (int)hidden_, out.as<float>(),
-                                     ctx.stream));
+                                     always.tensor.defined() ? always.tensor.as<float>() : nullptr, always.tensor.defined() ? always.splits : 0,
+                                     (long long)T * hidden_, ctx.stream));
         return Addend(out, 1);
     }
 
@@ -163,11 +223,14 @@ private:
     int64_t hidden_, inter_;
     int experts_, top_;
     GateSpec gate_;
-    bool has_bias_ = false;
+    bool gated_ = true, has_bias_ = false, has_correction_ = false;
+    int unary_ = 0, scoring_ = 0, groups_ = 1, keep_ = 1;
+    int64_t up_width_ = 0;
+    std::shared_ptr<FeedForward> shared_;
     std::vector<std::array<std::string, 3>> expert_names_;
     std::vector<Linear> expert_gate_up_, expert_down_;
     PinnedBuffer counts_host_;
-    Tensor router_, router_bias_, gate_up_, down_;
+    Tensor router_, router_bias_, correction_, gate_up_, down_;
 };
 
 void register_routed_parts() {

@@ -27,7 +27,10 @@ void check_folder(const SafetensorsFolder& folder, const std::vector<TensorSpec>
         wanted.insert(s.name);
         const TensorEntry* e = folder.find(s.name);
         if (!e) { err.missing.push_back(s.name); continue; }
-        if (e->shape != s.shape)
+        // a dimension of -1 in what a part announces stands for "as stored": the part reads the size when it binds
+        bool fits = e->shape.size() == s.shape.size();
+        for (size_t i = 0; fits && i < s.shape.size(); i++) fits = s.shape[i] < 0 || s.shape[i] == e->shape[i];
+        if (!fits)
             err.wrong_shape.push_back(s.name + " is " + shape_text(e->shape) + ", expected " + shape_text(s.shape));
         const bool ok = s.role == Role::Table ? dtype_is_int(e->dtype) : dtype_is_float(e->dtype);
         if (!ok) err.wrong_type.push_back(s.name + " is stored as " + e->dtype_name + ", which a " + role_name(s.role) + " cannot be");
@@ -131,6 +134,8 @@ Tensor RandomSource::fetch(const std::string& name) {
     auto sp = specs_.find(name);
     if (sp == specs_.end()) throw Error(kInvalidState, "a part asks for the tensor '" + name + "' that it did not announce");
     const TensorSpec& spec = sp->second;
+    for (int64_t d : spec.shape)
+        if (d < 0) throw ConfigError(name + ": a size that only a stored tensor gives cannot be drawn at random; the configuration must name it");
     int kind; double a, b;
     random_kind(spec, init_, kind, a, b);
     const DType stored = spec.role == Role::Matrix ? stored_ : DType::F32;
