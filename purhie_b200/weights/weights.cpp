@@ -190,6 +190,8 @@ void write_random_model(const std::string& model_dir, const ModelConfig& config,
     }
     std::vector<TensorToWrite> out;
     for (const TensorSpec& spec : expected_tensors(config)) {
+        for (int64_t d : spec.shape)
+            if (d < 0) throw ConfigError(spec.name + ": a size that only a stored tensor gives cannot be drawn at random; the configuration must name it");
         TensorToWrite t;
         t.name = spec.name;
         t.dtype = spec.role == Role::Matrix ? matrix_dtype : vector_dtype;

@@ -182,3 +182,47 @@ def test_slots_of_a_long_portion_are_those_of_its_tokens_one_by_one():
     assert cm.token_slots("a", 1, 300, 80) == sum((cm.token_slots("a", 1, p, 1) for p in range(300, 380)), [])
     with pytest.raises(RuntimeError):
         cm.token_slots("a", 1, 0, 100)
+
+
+def test_a_block_mask_gives_back_the_pages_in_front_of_the_current_block():
+    """Pages under a mask of blocks of 20 positions (counted from 0): once the next position lies in block b, nothing
+    before 20 b can be seen again, whatever the sizes of the steps; a window on top of it takes the later start."""
+    blocks = CacheNeed.pages(2, 16, chunk=20)
+    both = CacheNeed.pages(2, 16, window=12, chunk=20)
+    m = CacheManager([blocks, blocks, both, CacheNeed.pages(2, 16)], page_size=8, num_pages=[16, 16, 16], max_requests=2)
+    assert [(g["chunk"], g["window"], g["entries"]) for g in m.groups] == [(20, None, [0, 1]), (20, 12, [2]), (0, None, [3])]
+    m.add_request("a")
+    total = 0
+    for n in (5, 3, 11, 1, 1, 19, 1, 40, 2, 17):
+        m.reserve("a", n)
+        m.advance("a", n)
+        total += n
+        m.check()
+        start = total // 20 * 20                      # the first position that position `total` can see
+        for group, first in ((0, start), (1, max(start, total - 12 + 1))):
+            t = m.block_table("a", group)
+            assert all(p == -1 for p in t[:first // 8]) and all(p >= 0 for p in t[first // 8:])
+        assert all(p >= 0 for p in m.block_table("a", 2))
+    with pytest.raises(RuntimeError):
+        m.token_slots("a", 0, 0, 1)
+    assert len(set(m.token_slots("a", 0, total - 3, 3))) == 3
+    with pytest.raises(InferenceError):
+        m.truncate("a", 10)                           # what the mask has let go cannot be brought back
+    m.release("a")
+    assert m.free_pages() == [16, 16, 16]
+    m.check()
+
+
+def test_an_entry_may_keep_pages_and_a_state():
+    """Two mixers side by side in one layer: the pages of the one and the state of the other belong to one entry."""
+    both = CacheNeed.pages(1, 8, value_dim=4, chunk=16, state=(2, 3, 5))
+    m = CacheManager([both, CacheNeed.state((7,)), CacheNeed.pages(1, 8, value_dim=4, chunk=16)], page_size=4, num_pages=[8], max_requests=2)
+    assert m.state_entries == [0, 1] and m.entry_group == {0: 0, 2: 0}
+    m.add_request("a"); m.add_request("b")
+    with pytest.raises(OutOfSlots):
+        m.add_request("c")
+    assert m.slot_of("a") != m.slot_of("b")
+    m.reserve("a", 9); m.advance("a", 9)
+    m.release("a")
+    m.add_request("c")
+    m.check()
