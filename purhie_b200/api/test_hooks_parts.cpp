@@ -180,7 +180,7 @@ API const char* qe_part_cache_need(void* h) {
         j.set("head_dim", n.head_dim);
         if (n.kind == CacheNeed::Pages && n.value_dim) j.set("value_dim", n.value_dim);
         j.set("window", n.window ? Json(n.window) : Json());
-        j.set("chunk", n.chunk);
+        if (n.chunk) j.set("chunk", n.chunk);
         Json shape = Json::array();
         for (auto d : n.state_shape) shape.push((long long)d);
         j.set("state_shape", shape);

@@ -74,6 +74,13 @@ def draw_weights(cfg, seed, std=0.3):
         else:
             a = rng.normal(0.0, std, shape)
         out[name] = bf16_round(a.astype(np.float32))          # representable in either storage
+    # The right mixer's first tokens give o = v (k . q), and the head norm behind it keeps only the sign of k . q: with q
+    # and k drawn independently that product is a difference of like terms whose sign a bfloat16 rounding can turn.  Real
+    # models do not live there; q is drawn near k so that a token's own term is positive and leads.
+    for name in list(out):
+        if name.endswith("mix.right.q"):
+            k = out[name[:-1] + "k"]
+            out[name] = bf16_round((k + 0.5 * out[name]).astype(np.float32))
     return out
 
 

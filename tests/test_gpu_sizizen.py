@@ -418,7 +418,7 @@ def test_attention_under_a_block_mask_alone(models):
         assert kind == "side_by_side" and params["left"]["kind"] == "attention" and params["left"]["params"]["chunk"] == m["mask"]["size"]
         p = PartProbe("mixer", "attention", params["left"]["params"])
         p.bind_folder(folder)
-        assert p.cache_need()["chunk"] == m["mask"]["size"]
+        assert p.cache_need().get("chunk") == m["mask"]["size"]
         p.mixer_cache(8, 16, 2)
         close(mixer_in_pieces(p, x, [9, 1, 35]), ref, 1e-4)
         close(mixer_in_pieces(p, x, [1, 2, 2, 40]), ref, 1e-4)
