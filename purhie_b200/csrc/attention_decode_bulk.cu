@@ -49,7 +49,7 @@ struct BulkParams {
     float* part_o;
     float* part_ml;
     __nv_bfloat16* out;
-    int n_rows, HQ, HKV, splits, window;
+    int n_rows, HQ, HKV, splits, window, chunk;
     float scale_log2;
     int* error_flag;
 };
@@ -67,7 +67,7 @@ __device__ __forceinline__ Item make_item(const BulkParams& p, int w) {
     it.i = rest / p.HKV;
     it.t = p.row_list ? p.row_list[it.i] : it.i;
     it.z = p.positions[it.t];
-    it.lo = p.window > 0 ? max(0, it.z - p.window + 1) : 0;
+    it.lo = first_seen(it.z, p.window, p.chunk);
     it.lo_page = it.lo - it.lo % p.page_size;
     const int n_blocks = (it.z - it.lo_page) / BLOCK_KEYS + 1;
     it.n_blocks = n_blocks;
@@ -512,10 +512,10 @@ PH_EXPORT int ph_attention_decode_bulk(const void* q, const void* k_base, const 
                                        int page_size, int num_pages, const int32_t* block_table, int table_stride,
                                        const int32_t* row_list, int n_rows, const int32_t* row_seg,
                                        const int32_t* positions, float* part_o, float* part_ml, void* out, int HQ,
-                                       int HKV, int D, int splits, int window, float scale, int max_ctas,
+                                       int HKV, int D, int splits, int window, int chunk, float scale, int max_ctas,
                                        int* error_flag, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || !error_flag || n_rows < 0 ||
-        HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || num_pages < 1 || window < 0 || splits < 1 ||
+        HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || num_pages < 1 || window < 0 || chunk < 0 || splits < 1 ||
         (splits > 1 && (!part_o || !part_ml)))
         return fail(PH_ERR_ARG, "attention_decode_bulk: bad arguments (rows %d, HQ %d, HKV %d, splits %d)", n_rows, HQ, HKV, splits);
     if (D != 64 && D != 128) return fail(PH_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d is not 64 or 128", D);
@@ -542,7 +542,7 @@ PH_EXPORT int ph_attention_decode_bulk(const void* q, const void* k_base, const 
     p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
     p.block_table = block_table; p.table_stride = table_stride;
     p.row_list = row_list; p.row_seg = row_seg; p.positions = positions; p.part_o = part_o; p.part_ml = part_ml;
-    p.out = (__nv_bfloat16*)out; p.n_rows = n_rows; p.HQ = HQ; p.HKV = HKV; p.splits = splits; p.window = window;
+    p.out = (__nv_bfloat16*)out; p.n_rows = n_rows; p.HQ = HQ; p.HKV = HKV; p.splits = splits; p.window = window; p.chunk = chunk;
     p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
     return D == 64 ? launch_bulk<64>(mkv, p, max_ctas, stream) : launch_bulk<128>(mkv, p, max_ctas, stream);
 }

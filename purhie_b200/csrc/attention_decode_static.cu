@@ -62,5 +62,5 @@ PH_EXPORT int ph_attention_decode_static(const void* q, const void* k_base, cons
     float* part_o = scratch;
     float* part_ml = scratch + slots * (unsigned long long)D;        // D is a multiple of 16: stays 8-byte aligned
     return ph_attention_decode(q, k_base, v_base, page_stride, page_size, block_table, table_stride, row_list, n_rows,
-                               row_seg, positions, part_o, part_ml, out, HQ, HKV, D, splits, window, scale, stream);
+                               row_seg, positions, part_o, part_ml, out, HQ, HKV, D, splits, window, 0, scale, stream);
 }

@@ -9,7 +9,7 @@
 // Keys and values are gathered from pages with 16-byte cp.async copies into swizzled shared memory, two
 // blocks in flight; rows outside the visible range are zero-filled, so whatever an unwritten or reused page
 // holds (NaN included) never reaches a product.  A row at absolute position z sees positions
-// max(0, z - window + 1) .. z (window 0: all of them).
+// max(0, z - window + 1) .. z (window 0: all of them), and with a mask of blocks (chunk > 0) nothing before its own block.
 // Math as in the reference: src/attention.hip:612-701 (flash tiles, online softmax), :315-443 (partial
 // results per chunk and their combination), scale 1/sqrt(D) applied to the scores (src/attention.cpp:197).
 #include "attention_mma.cuh"
@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_base, const __nv_bfloat16* __restrict__ v_base,
     long long page_stride, int page_size, const int32_t* __restrict__ block_table, int table_stride,
     const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_ctx_len, const int32_t* __restrict__ tile_seg,
-    const int32_t* __restrict__ tile_first, __nv_bfloat16* __restrict__ out, int HQ, int HKV, int window, float scale_log2) {
+    const int32_t* __restrict__ tile_first, __nv_bfloat16* __restrict__ out, int HQ, int HKV, int window, int chunk, float scale_log2) {
     constexpr int BM = 64;
     constexpr int TILE_BYTES = BLOCK_KEYS * D * 2;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
             cp_async16(q_tile + tile_off<D>(r, chunk), src, valid);
         }
     }
-    const int lo_tile = window > 0 ? max(0, z_first - window + 1) : 0;
+    const int lo_tile = first_seen(z_first, window, chunk);
     const int kb_first = lo_tile / BLOCK_KEYS, kb_last = z_last / BLOCK_KEYS;
     load_kv_block<D>(kv, kb_first * BLOCK_KEYS, lo_tile, z_last, kv_tiles, kv_tiles + TILE_BYTES);
     cp_async_commit();
@@ -62,9 +62,9 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
     // this thread's two rows
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
     const int z0 = z_first + min(r0, n_rows - 1), z1 = z_first + min(r1, n_rows - 1);
-    const int lo0 = window > 0 ? max(0, z0 - window + 1) : 0, lo1 = window > 0 ? max(0, z1 - window + 1) : 0;
+    const int lo0 = first_seen(z0, window, chunk), lo1 = first_seen(z1, window, chunk);
     const int warp_zmin = z_first + min(warp * 16, n_rows - 1), warp_zmax = z_first + min(warp * 16 + 15, n_rows - 1);
-    const int warp_lomax = window > 0 ? max(0, warp_zmax - window + 1) : 0;
+    const int warp_lomax = first_seen(warp_zmax, window, chunk);
 
     uint32_t qf[D / 16][4];
     float o[D / 8][4];
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
         }
         const int key0 = kb * BLOCK_KEYS;
         // a warp skips blocks none of its rows can see
-        if (key0 <= warp_zmax && key0 + BLOCK_KEYS - 1 >= (window > 0 ? max(0, warp_zmin - window + 1) : 0)) {
+        if (key0 <= warp_zmax && key0 + BLOCK_KEYS - 1 >= (first_seen(warp_zmin, window, chunk))) {
             float s[BLOCK_KEYS / 8][4];
             warp_qk<D, BLOCK_KEYS>(qf, k_tile, 0, s);
             const bool need_mask = key0 + BLOCK_KEYS - 1 > warp_zmin || key0 < warp_lomax;
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     long long page_stride, int page_size, const int32_t* __restrict__ block_table, int table_stride,
     const int32_t* __restrict__ row_list, const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int HQ, int HKV, int splits,
-    int window, float scale_log2) {
+    int window, int chunk, float scale_log2) {
     constexpr int TILE_BYTES = BLOCK_KEYS * D * 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t q_tile = smem_u32(smem);                     // 16 x D
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     const int G = HQ / HKV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int z = positions[t];
-    const int lo = window > 0 ? max(0, z - window + 1) : 0;
+    const int lo = first_seen(z, window, chunk);
     const int n_blocks = (z - lo) / BLOCK_KEYS + 1;
     const int per = (n_blocks + splits - 1) / splits;
     const int b_first = split * per, b_last = min(n_blocks, b_first + per) - 1;
@@ -272,10 +272,10 @@ PH_DEFINE_LAST_ERROR(ph_flash)
 PH_EXPORT int ph_attention_prefill(const void* q, const void* k_base, const void* v_base, long long page_stride,
                                    int page_size, const int32_t* block_table, int table_stride, const int32_t* seg_start,
                                    const int32_t* seg_ctx_len, const int32_t* tile_seg, const int32_t* tile_first,
-                                   int n_tiles, void* out, int HQ, int HKV, int D, int window, float scale,
+                                   int n_tiles, void* out, int HQ, int HKV, int D, int window, int chunk, float scale,
                                    cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out ||
-        n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || window < 0)
+        n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || window < 0 || chunk < 0)
         return fail(PH_ERR_ARG, "attention_prefill: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
     if (D != 64 && D != 128) return fail(PH_ERR_UNSUPPORTED, "attention_prefill: head_dim %d is not 64 or 128", D);
     if (n_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill: %d tiles exceed the grid", n_tiles);
@@ -289,7 +289,7 @@ PH_EXPORT int ph_attention_prefill(const void* q, const void* k_base, const void
         attention_prefill_kernel<DD><<<grid, THREADS, bytes, stream>>>(                                          \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_base, (const __nv_bfloat16*)v_base, page_stride,    \
             page_size, block_table, table_stride, seg_start, seg_ctx_len, tile_seg, tile_first,                  \
-            (__nv_bfloat16*)out, HQ, HKV, window, scale_log2);                                                   \
+            (__nv_bfloat16*)out, HQ, HKV, window, chunk, scale_log2);                                                   \
     } while (0)
     if (D == 64) LAUNCH(64); else LAUNCH(128);
 #undef LAUNCH
@@ -299,10 +299,10 @@ PH_EXPORT int ph_attention_prefill(const void* q, const void* k_base, const void
 PH_EXPORT int ph_attention_decode(const void* q, const void* k_base, const void* v_base, long long page_stride,
                                   int page_size, const int32_t* block_table, int table_stride, const int32_t* row_list,
                                   int n_rows, const int32_t* row_seg, const int32_t* positions, float* part_o,
-                                  float* part_ml, void* out, int HQ, int HKV, int D, int splits, int window, float scale,
+                                  float* part_ml, void* out, int HQ, int HKV, int D, int splits, int window, int chunk, float scale,
                                   cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || n_rows < 0 || HQ < 1 || HKV < 1 ||
-        HQ % HKV || page_size < 1 || window < 0 || splits < 1 || (splits > 1 && (!part_o || !part_ml)))
+        HQ % HKV || page_size < 1 || window < 0 || chunk < 0 || splits < 1 || (splits > 1 && (!part_o || !part_ml)))
         return fail(PH_ERR_ARG, "attention_decode: bad arguments (rows %d, HQ %d, HKV %d, splits %d)", n_rows, HQ, HKV, splits);
     if (D != 64 && D != 128) return fail(PH_ERR_UNSUPPORTED, "attention_decode: head_dim %d is not 64 or 128", D);
     if (HQ / HKV > 16) return fail(PH_ERR_UNSUPPORTED, "attention_decode: %d query heads per kv head exceed 16", HQ / HKV);
@@ -318,7 +318,7 @@ PH_EXPORT int ph_attention_decode(const void* q, const void* k_base, const void*
         attention_decode_kernel<DD><<<grid, THREADS, bytes, stream>>>(                                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_base, (const __nv_bfloat16*)v_base, page_stride,    \
             page_size, block_table, table_stride, row_list, row_seg, positions, part_o, part_ml,                 \
-            (__nv_bfloat16*)out, HQ, HKV, splits, window, scale_log2);                                           \
+            (__nv_bfloat16*)out, HQ, HKV, splits, window, chunk, scale_log2);                                           \
         if (splits > 1)                                                                                          \
             attention_combine_kernel<DD><<<dim3(n_rows, HQ), DD < 128 ? DD : 128, 0, stream>>>(                  \
                 part_o, part_ml, row_list, (__nv_bfloat16*)out, HQ, splits);                                     \

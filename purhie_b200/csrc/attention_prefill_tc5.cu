@@ -17,7 +17,8 @@
 // Tensor memory: columns 0-63 scores (then P) of even blocks, 64-191 O, 192-255 scores of odd blocks.
 // A tile's keys may be shared by several CTAs (grid z), for a few tiles late in a long context: each leaves its
 // unnormalised sums, its reference and its row sums in scratch, and a second kernel merges them.
-// A row at absolute position z sees positions max(0, z - window + 1) .. z.  Pages past the tile's last token
+// A row at absolute position z sees positions max(0, z - window + 1) .. z (with a mask of blocks of `chunk` positions,
+// nothing before its own block).  Pages past the tile's last token
 // come from an out-of-range coordinate (zeros), scores of invisible keys are replaced by -inf and value rows
 // after the last token inside its page are zeroed before P V, so unwritten page slots may hold anything.
 // Every mbarrier wait is bounded and reports through an error word; TMEM is freed on every path.
@@ -67,7 +68,7 @@ struct Tc5Params {
     const int32_t* tile_first;
     int n_tiles;
     __nv_bfloat16* out;
-    int HQ, HKV, window;
+    int HQ, HKV, window, chunk;
     float scale_log2;
     int* error_flag;
     int splits;                    // CTAs that share a tile's keys (grid z); > 1: partial results, merged by a second kernel
@@ -212,7 +213,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int ctx_len = p.seg_ctx_len[seg];
     const int n_rows = min(BM, q_len - first);
     const int z_first = ctx_len - q_len + first, z_last = z_first + n_rows - 1;
-    const int lo_tile = p.window > 0 ? max(0, z_first - p.window + 1) : 0;
+    const int lo_tile = first_seen(z_first, p.window, p.chunk);
     const int lo_page = lo_tile - (lo_tile & (p.page_size - 1));
     const int tile_blocks = (z_last - lo_page) / BN + 1;          // blocks of 64 keys the tile sees
     // this CTA's share of them: blocks b_first .. b_first + n_blocks - 1 (none when the tile has fewer blocks than CTAs)
@@ -346,7 +347,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int q = warp & 3;                          // TMEM lane quarter of this warp
         const int r = q * 32 + lane;                     // row of the tile
         const int z = z_first + min(r, n_rows - 1);      // rows past the portion repeat the last one; never stored
-        const int lo = p.window > 0 ? max(0, z - p.window + 1) : 0;
+        const int lo = first_seen(z, p.window, p.chunk);
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         float m_ref = -INFINITY;                         // the maximum the exponents refer to
         float l = 0.0f;
@@ -585,10 +586,10 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
                                        int page_size, int num_pages, const int32_t* block_table, int table_stride,
                                        const int32_t* seg_start, const int32_t* seg_ctx_len, const int32_t* tile_seg,
                                        const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
-                                       int window, float scale, int splits, float* part_o, float* part_ml,
+                                       int window, int chunk, float scale, int splits, float* part_o, float* part_ml,
                                        int* error_flag, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out ||
-        !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || !(scale > 0.0f))
+        !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || chunk < 0 || !(scale > 0.0f))
         return fail(PH_ERR_ARG, "attention_prefill_tc5: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
     if (head_dim != D) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: head_dim %d is not %d", head_dim, D);
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
@@ -618,7 +619,7 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
     p.rows_per_page = rows_per_page; p.total_rows = (int)rows; p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
     p.block_table = block_table; p.table_stride = table_stride; p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len;
     p.tile_seg = tile_seg; p.tile_first = tile_first; p.n_tiles = n_tiles; p.out = (__nv_bfloat16*)out;
-    p.HQ = HQ; p.HKV = HKV; p.window = window; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
+    p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
     p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
     static bool configured = false;
     if (!configured) {

@@ -83,6 +83,17 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The first position that the position z sees: z - window + 1 under a window of `window` positions (0: none), and not
+// before the start of z's own block under a mask of blocks of `chunk` positions counted from 0 (0: none).
+__device__ __forceinline__ int first_seen(int z, int window, int chunk) {
+    int lo = (window > 0 && z - window + 1 > 0) ? z - window + 1 : 0;
+    if (chunk > 0) {
+        const int start = z / chunk * chunk;
+        if (start > lo) lo = start;
+    }
+    return lo;
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

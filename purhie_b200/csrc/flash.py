@@ -16,15 +16,15 @@ from .ops import KernelError, call, register_signatures
 
 register_signatures("flash", {
     "ph_attention_prefill": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "ph_attention_decode_bulk": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
-                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_int, c_void_p, c_void_p],
     "ph_attention_prefill_tc5": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
-                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "ph_attention_decode": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                             c_void_p],
 })
 
@@ -69,11 +69,11 @@ def decode_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window
 
 
 def prefill(q, k_base, v_base, page_stride, page_size, block_table, seg_start, seg_ctx_len, tile_seg, tile_first,
-            n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+            n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale, chunk: int = 0) -> None:
     call("flash", "ph_attention_prefill", q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), page_stride, page_size,
          block_table.data_ptr(), block_table.shape[-1], seg_start.data_ptr(), seg_ctx_len.data_ptr(), tile_seg.data_ptr(),
-         tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim, int(window or 0), float(scale),
-         ops._stream())
+         tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim, int(window or 0), int(chunk),
+         float(scale), ops._stream())
 
 
 def tc5_supports(head_dim: int, page_size: int) -> bool:
@@ -101,7 +101,7 @@ def tc5_splits(n_tiles: int, num_heads: int, max_ctx: int, sms: int, window: Opt
 
 
 def prefill_tc5(q, n_rows, k_base, v_base, page_stride, page_size, num_pages, block_table, seg_start, seg_ctx_len, tile_seg,
-                tile_first, n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale, splits: int = 1,
+                tile_first, n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale, splits: int = 1, chunk: int = 0,
                 workspace=None) -> None:
     """The tcgen05 prefill kernel (attention_prefill_tc5.cu); tiles of 128 rows, each shared by ``splits`` CTAs."""
     part_o = part_ml = None
@@ -111,12 +111,12 @@ def prefill_tc5(q, n_rows, k_base, v_base, page_stride, page_size, num_pages, bl
     call("flash", "ph_attention_prefill_tc5", q.data_ptr(), n_rows, k_base.data_ptr(), v_base.data_ptr(), page_stride,
          page_size, num_pages, block_table.data_ptr(), block_table.shape[-1], seg_start.data_ptr(), seg_ctx_len.data_ptr(),
          tile_seg.data_ptr(), tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim,
-         int(window or 0), float(scale), splits, None if part_o is None else part_o.data_ptr(),
+         int(window or 0), int(chunk), float(scale), splits, None if part_o is None else part_o.data_ptr(),
          None if part_ml is None else part_ml.data_ptr(), error_flag(q.device).data_ptr(), ops._stream())
 
 
 def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_rows, row_seg, positions, out, workspace, *,
-           num_heads, num_kv_heads, head_dim, window, scale, splits) -> None:
+           num_heads, num_kv_heads, head_dim, window, scale, splits, chunk: int = 0) -> None:
     part_o = part_ml = None
     if splits > 1:
         part_o = workspace.get("attn_part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
@@ -125,7 +125,7 @@ def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_r
          block_table.data_ptr(), block_table.shape[-1], None if row_list is None else row_list.data_ptr(), n_rows,
          row_seg.data_ptr(), positions.data_ptr(), None if part_o is None else part_o.data_ptr(),
          None if part_ml is None else part_ml.data_ptr(), out.data_ptr(), num_heads, num_kv_heads, head_dim, splits,
-         int(window or 0), float(scale), ops._stream())
+         int(window or 0), int(chunk), float(scale), ops._stream())
 
 
 _flags = {}
@@ -177,7 +177,7 @@ def bulk_supports(page_size: int) -> bool:
 
 
 def decode_bulk(q, k_base, v_base, page_stride, page_size, num_pages, block_table, row_list, n_rows, row_seg, positions, out,
-                workspace, *, num_heads, num_kv_heads, head_dim, window, scale, splits, max_ctas: int = 0) -> None:
+                workspace, *, num_heads, num_kv_heads, head_dim, window, scale, splits, max_ctas: int = 0, chunk: int = 0) -> None:
     """The persistent decode kernel fed by TMA copies of whole pages (attention_decode_bulk.cu)."""
     part_o = part_ml = None
     if splits > 1:
@@ -187,4 +187,4 @@ def decode_bulk(q, k_base, v_base, page_stride, page_size, num_pages, block_tabl
          num_pages, block_table.data_ptr(), block_table.shape[-1], None if row_list is None else row_list.data_ptr(), n_rows,
          row_seg.data_ptr(), positions.data_ptr(), None if part_o is None else part_o.data_ptr(),
          None if part_ml is None else part_ml.data_ptr(), out.data_ptr(), num_heads, num_kv_heads, head_dim, splits,
-         int(window or 0), float(scale), max_ctas, error_flag(q.device).data_ptr(), ops._stream())
+         int(window or 0), int(chunk), float(scale), max_ctas, error_flag(q.device).data_ptr(), ops._stream())

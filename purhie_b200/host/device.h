@@ -144,14 +144,14 @@ struct CoreKernels {
 };
 struct FlashKernels {
     int (*prefill)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*,
-                   const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, float, cudaStream_t);
+                   const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, int, float, cudaStream_t);
     int (*decode)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*, int,
-                  const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, float, cudaStream_t);
+                  const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, int, float, cudaStream_t);
     int (*decode_bulk)(const void*, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*, int,
-                       const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, float, int, int*,
+                       const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, int, float, int, int*,
                        cudaStream_t);
     int (*prefill_tc5)(const void*, int, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*,
-                       const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, float, int, float*,
+                       const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, int, float, int, float*,
                        float*, int*, cudaStream_t);
     const char* (*last_error)(void);
 };

@@ -227,9 +227,11 @@ public:
     // rows per tile of the products for many tokens (the tcgen05 pair kernel): a scheduler may end a step there
     int preferred_row_multiple() const override { return (qkv_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
 
+    // how far back a row can look at most: the window, the mask's block, the smaller of the two (0: all the way)
+    int reach() const { return window_ && chunk_ ? std::min(window_, chunk_) : window_ ? window_ : chunk_; }
+
     bool use_flash() const {
         if (compute_dtype != DType::BF16 || attention_ == "generic") return false;
-        if (chunk_) return false;                 // the block mask is the plain kernel's
         const int group = heads_ / kv_heads_;
         const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16;
         if (!ok && attention_ == "flash")
@@ -302,7 +304,7 @@ public:
             double seen = 0.0, read = 0.0;
             for (size_t i = 0; i < ctx.q_lens.size(); i++) {
                 const double n = ctx.q_lens[i], len = ctx.ctx_lens[i];
-                const int reach = chunk_ ? (window_ ? std::min(window_, chunk_) : chunk_) : window_;
+                const int reach = this->reach();
                 const double span = reach ? std::min<double>(len, reach + n) : len;
                 read += span;
                 seen += reach ? n * std::min<double>(len, chunk_ ? reach / 2.0 : reach) : n * (len - n) + n * (n + 1) / 2.0;
@@ -334,7 +336,7 @@ private:
         const bool tc5_ok = head_dim_ == 128 && (cache.page_size == 8 || cache.page_size == 16 || cache.page_size == 32 || cache.page_size == 64) && cache.num_pages > 0;
         if (t64.count && t128.count && tc5_ok && ctx.option("prefill_kernel") != "mma_sync") {
             int splits = (int)ctx.option_int("prefill_splits");
-            if (!splits) splits = tc5_splits(t128.count, heads_, ctx.prefill_max_ctx, sms, window_);
+            if (!splits) splits = tc5_splits(t128.count, heads_, ctx.prefill_max_ctx, sms, reach());
             float *part_o = nullptr, *part_ml = nullptr;
             if (splits > 1) {
                 part_o = ws.get("attn_tile_part_o", {ctx.T, heads_, splits, head_dim_}, DType::F32).as<float>();
@@ -342,12 +344,12 @@ private:
             }
             QE_LAUNCH(f, f.prefill_tc5(q.data, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
                                        g.block_table, g.table_width, ctx.seg_start, ctx.seg_ctx_len, t128.data, t128f.data, t128.count,
-                                       out.data, heads_, kv_heads_, head_dim_, window_, (float)scale_, splits, part_o, part_ml,
+                                       out.data, heads_, kv_heads_, head_dim_, window_, chunk_, (float)scale_, splits, part_o, part_ml,
                                        ctx.attention_error, ctx.stream));
         } else if (t64.count) {
             QE_LAUNCH(f, f.prefill(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table, g.table_width,
                                    ctx.seg_start, ctx.seg_ctx_len, t64.data, t64f.data, t64.count, out.data, heads_, kv_heads_,
-                                   head_dim_, window_, (float)scale_, ctx.stream));
+                                   head_dim_, window_, chunk_, (float)scale_, ctx.stream));
         }
         if (!ctx.n_decode_rows) return;
         const int n = ctx.n_decode_rows;
@@ -355,8 +357,8 @@ private:
         const bool bulk = bulk_ok && ctx.option("decode_kernel") != "cp_async";
         int splits = (int)ctx.option_int("decode_splits");            // a test's choice, else what the cost model picks
         if (splits < 1 || splits > kMaxSplits)
-            splits = bulk ? bulk_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_)
-                          : decode_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_);
+            splits = bulk ? bulk_splits(n, kv_heads_, ctx.decode_max_ctx, sms, reach())
+                          : decode_splits(n, kv_heads_, ctx.decode_max_ctx, sms, reach());
         float *part_o = nullptr, *part_ml = nullptr;
         if (splits > 1) {
             part_o = ws.get("attn_part_o", {n, heads_, splits, head_dim_}, DType::F32).as<float>();
@@ -365,11 +367,11 @@ private:
         if (bulk)
             QE_LAUNCH(f, f.decode_bulk(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages, g.block_table,
                                        g.table_width, ctx.decode_rows, n, ctx.row_seg, positions, part_o, part_ml, out.data, heads_,
-                                       kv_heads_, head_dim_, splits, window_, (float)scale_, 0, ctx.attention_error, ctx.stream));
+                                       kv_heads_, head_dim_, splits, window_, chunk_, (float)scale_, 0, ctx.attention_error, ctx.stream));
         else
             QE_LAUNCH(f, f.decode(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table, g.table_width,
                                   ctx.decode_rows, n, ctx.row_seg, positions, part_o, part_ml, out.data, heads_, kv_heads_, head_dim_,
-                                  splits, window_, (float)scale_, ctx.stream));
+                                  splits, window_, chunk_, (float)scale_, ctx.stream));
     }
 
     int64_t hidden_, q_width_, kv_width_, v_width_, o_width_;

@@ -512,7 +512,7 @@ def paged_case(segs, HQ, HKV, D, page_size, dtype, seed=0, poison=True):
                 seg_ctx=i32([c for c, _ in segs]), dense=dense, T=T, segs=segs)
 
 
-def dense_attention(case, HQ, HKV, D, window, scale):
+def dense_attention(case, HQ, HKV, D, window, scale, chunk=0):
     out = torch.zeros(case["T"], HQ, D, dtype=torch.float64)
     row = 0
     for (ctx, ql), (k, v) in zip(case["segs"], case["dense"]):
@@ -520,6 +520,8 @@ def dense_attention(case, HQ, HKV, D, window, scale):
         for i in range(ql):
             z = ctx - ql + i
             lo = max(0, z - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, z // chunk * chunk)
             for h in range(HQ):
                 g = h // (HQ // HKV)
                 s = (k[lo:z + 1, g] @ case["q"][row, h].double().cpu()) * scale
@@ -529,16 +531,16 @@ def dense_attention(case, HQ, HKV, D, window, scale):
     return out.view(case["T"], HQ * D)
 
 
-def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
+def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype, chunk=0):
     from purhie_b200.csrc import ops
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=out_dtype, device=DEV)
     ops.attention_generic(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
                           case["row_seg"], case["positions"], out, num_heads=HQ, num_kv_heads=HKV, head_dim=D,
-                          window=window, scale=scale)
+                          window=window, scale=scale, chunk=chunk)
     return out
 
 
-def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True, tile_splits=1):
+def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True, tile_splits=1, chunk=0):
     from purhie_b200.csrc import flash
     from purhie_b200.csrc.ops import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -556,19 +558,19 @@ def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True
         flash.prefill_tc5(case["q"], case["T"], case["k_base"], case["v_base"], case["page_stride"], page_size,
                           case["pool"].shape[0], case["table"], case["seg_start"], case["seg_ctx"], i32([b[0] for b in big]),
                           i32([b[1] for b in big]), len(big), out, num_heads=HQ, num_kv_heads=HKV, head_dim=D,
-                          window=window, scale=scale, splits=tile_splits, workspace=Workspace(DEV))
+                          window=window, scale=scale, splits=tile_splits, workspace=Workspace(DEV), chunk=chunk)
         flash.check_errors(DEV)
     elif tile_seg:
         flash.prefill(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
                       case["seg_start"], case["seg_ctx"], i32(tile_seg), i32(tile_first), len(tile_seg), out,
-                      num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
+                      num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale, chunk=chunk)
     if dec_rows:
         max_ctx = max(c for c, ql in case["segs"] if ql == 1)
         head = (case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size)
         tail = (case["table"], None if len(dec_rows) == case["T"] else i32(dec_rows), len(dec_rows), case["row_seg"],
                 case["positions"], out, Workspace(DEV))
         args = head + tail
-        kw = dict(num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
+        kw = dict(num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale, chunk=chunk)
         if bulk and flash.bulk_supports(page_size):
             sp = splits or flash.bulk_splits(len(dec_rows), HKV, max_ctx, 148, window)
             flash.decode_bulk(*head, case["pool"].shape[0], *tail, splits=sp, max_ctas=max_ctas, **kw)
@@ -706,6 +708,62 @@ def test_attention_window_edge_between_two_matching_keys(kernel, kw):
                 assert (got - 7.0).abs().max() < 0.05, (kernel, kw, window, ql, which, float(got.mean()))
                 ref = dense_attention(case, HQ, HKV, D, window, scale)
                 assert rel(out.cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("kernel,kw", [
+    ("generic", {}), ("bulk", {"splits": 1}), ("bulk", {"splits": 3}), ("cp_async", {"splits": 1}), ("cp_async", {"splits": 4}),
+    ("tc5", {"tile_splits": 1}), ("tc5", {"tile_splits": 3}), ("mma", {})])
+def test_attention_block_mask_edge_between_two_matching_keys(kernel, kw):
+    """Under a mask of blocks of `chunk` positions counted from 0, two keys match the query equally: the last one of the
+    block in front (value 3) and the first one of the query's own block (value 7).  The right answer is 7.  The block's
+    start is put inside a page, on a page's first slot and on a 64-key boundary; the query is a decode row, a row of a
+    2-token portion, and the first and last row of portions that begin in the block in front (so that one tile holds rows
+    of two blocks) or cover several blocks; a window on top of the mask takes the later start."""
+    HQ, HKV, D, ps = 4, 2, 128, 16
+    scale = 1.0 / math.sqrt(D)
+    dtype = torch.bfloat16
+    ctx = 600
+    decode = kernel in ("bulk", "cp_async")
+    for chunk, window in ((100, None), (64, None), (48, None), (200, None), (599, None), (100, 300), (300, 40)):
+        for ql in ((1,) if decode else (1, 2, 90, 200) if kernel == "generic" else (2, 90, 200)):
+            for which in sorted({0, ql - 1}):     # the portion's first and last row
+                case = paged_case([(ctx, ql)], HQ, HKV, D, ps, dtype, seed=4)
+                k, v = case["dense"][0]
+                z = ctx - ql + which
+                start = z // chunk * chunk
+                if window and z - window + 1 > start:
+                    start = z - window + 1
+                if start == 0 or start == z:
+                    continue
+                spike = torch.zeros(D, device=DEV); spike[9] = 60.0
+                case["q"][which, :] = spike.to(dtype)
+                for key_pos, value in ((start - 1, 3.0), (start, 7.0)):
+                    page, off = int(case["table"][0, key_pos // ps]), key_pos % ps
+                    case["pool"][page, 0, 0, :, off] = spike.to(dtype)
+                    case["pool"][page, 0, 1, :, off] = value
+                    k[key_pos] = spike.to(dtype)
+                    v[key_pos] = value
+                if kernel == "generic":
+                    out = run_generic(case, HQ, HKV, D, ps, window, scale, dtype, chunk=chunk)
+                else:
+                    out = run_flash(case, HQ, HKV, D, ps, window, scale, bulk=kernel != "cp_async", tc5=kernel != "mma", chunk=chunk, **kw)
+                got = out[which].float()
+                assert (got - 7.0).abs().max() < 0.05, (kernel, kw, chunk, window, ql, which, float(got.mean()))
+                ref = dense_attention(case, HQ, HKV, D, window, scale, chunk=chunk)
+                assert rel(out.cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("HQ,HKV,D,page_size,chunk", [(4, 2, 64, 16, 40), (8, 2, 128, 16, 128), (4, 4, 128, 32, 77), (6, 1, 64, 8, 500)])
+def test_attention_under_a_block_mask_in_mixed_batches(HQ, HKV, D, page_size, chunk):
+    """Prompt portions and decode rows of unequal requests in one call, masked by blocks: every tensor-core kernel and the
+    plain one against dense attention."""
+    scale = 0.7 / math.sqrt(D)
+    case = paged_case([(300, 300), (517, 1), (130, 2), (64, 1), (450, 129), (41, 1)], HQ, HKV, D, page_size, torch.bfloat16, seed=7)
+    ref = dense_attention(case, HQ, HKV, D, None, scale, chunk=chunk)
+    assert rel(run_generic(case, HQ, HKV, D, page_size, None, scale, torch.bfloat16, chunk=chunk).cpu(), ref) < 1e-2
+    assert rel(run_flash(case, HQ, HKV, D, page_size, None, scale, chunk=chunk).cpu(), ref) < 1e-2
+    assert rel(run_flash(case, HQ, HKV, D, page_size, None, scale, chunk=chunk, tc5=False, bulk=False, splits=2).cpu(), ref) < 1e-2
+    assert rel(run_flash(case, HQ, HKV, D, page_size, None, scale, chunk=chunk, splits=3, tile_splits=2).cpu(), ref) < 1e-2
 
 
 # ---- per-head norm, rotation and cache write ---------------------------------------------------------------
