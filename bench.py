@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
-    python bench.py --design bozosun [--size 2k|4k]      (another design beside the Qwen3 layers of equal size; see below)
+    python bench.py --design bozosun|sizizen [--size 2k|4k]   (another design beside the Qwen3 layers of equal size; see below)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on the
 device (CUDA events on the engine's stream) over exactly K decode steps after W warm-up steps, each step fed its
@@ -118,6 +118,23 @@ def bozosun_config(z):
             "embedding": {"scale": 1.0}, "layers": layers, "max_position": CONTEXT}
 
 
+def sizizen_config(z):
+    """Four layers of two mixers side by side (attention under a mask of blocks of 1,024 positions with heads of 128
+    rotated over half their width; gated linear attention with half as many heads of 128 x 128 state), a dense gated unit
+    in the first and last, routed ungated experts with a shared one in between."""
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "rot": {"base": 5e5, "dims": z["dim"] // 2},
+            "mask": {"size": 1024}, "scale": z["dim"] ** -0.5}
+    right = {"heads": z["heads"] // 2, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": z["expert_ff"]}}
+    layers = [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp} for mlp in (dense, moe, moe, dense)]
+    return {"architecture": "Sizizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers, "max_position": CONTEXT}
+
+
+DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config}
+
+
 def design_bench(args):
     """Prefill and decode throughput of the design at real layer sizes beside its twin, and, kernel class by kernel
     class, the time per call with the fraction of the roofline (bytes over the copy bandwidth or flops over the
@@ -131,9 +148,9 @@ def design_bench(args):
                 num_key_value_heads=z["kv_heads"], head_dim=z["dim"], vocab_size=z["vocab"])
     rng = np.random.default_rng(5)
     batch, steps, warmup = args.batch, min(args.steps, 32), max(args.warmup, 3)
-    result = {"design": "bozosun", "size": args.size, "sizes": z, "batch": batch, "prefix": PREFIX, "prefill_tokens": PREFILL_TOKENS,
+    result = {"design": args.design, "size": args.size, "sizes": z, "batch": batch, "prefix": PREFIX, "prefill_tokens": PREFILL_TOKENS,
               "peaks": pk, "models": {}}
-    for name, config in (("bozosun", bozosun_config(z)), ("qwen3_twin", twin)):
+    for name, config in ((args.design, DESIGN_CONFIGS[args.design](z)), ("qwen3_twin", twin)):
         vocab = z["vocab"]
         ids = lambda n: rng.integers(0, vocab, size=n).tolist()
         eng = Engine.from_random(config, 3, "bfloat16", std=0.02, page_size=16, max_requests=batch + 2,
@@ -205,7 +222,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the benchmark's configuration has 16)")
     ap.add_argument("--step-options", default="", metavar="JSON",
                     help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
-    ap.add_argument("--design", default="", choices=["", "bozosun"],
+    ap.add_argument("--design", default="", choices=["", "bozosun", "sizizen"],
                     help="instead of the headline workload: prefill and decode of this design at real layer sizes beside four "
                          "Qwen3 layers of equal size, with the time and roofline fraction of every kernel class")
     ap.add_argument("--size", default="4k", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")

@@ -118,8 +118,8 @@ struct CoreKernels {
     // gated linear attention: the decayed matrix state token by token with the head norm and gate behind it; two mixers'
     // outputs, each RMS-normed over the width, combined
     int (*decayed_scan)(const void*, const void*, const void*, const void*, int, long long, const float*, long long, const float*, float,
-                        float, const float*, float, float*, long long, const int32_t*, const int32_t*, int, int, int, int, int, float*,
-                        void*, cudaStream_t);
+                        float, const float*, float, float*, long long, const int32_t*, const int32_t*, int, int, int, int, int,
+                        const int32_t*, int, const int32_t*, float*, float*, float*, void*, cudaStream_t);
     int (*rms_pair_mean)(const void*, int, int, long long, const float*, const void*, int, int, long long, const float*, float, float,
                          float*, int, int, cudaStream_t);
     // selective state-space mixer: convolution + silu, and the scan

@@ -82,10 +82,38 @@ public:
     }
     int preferred_row_multiple() const override { return (qkvg_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
 
-    CacheNeed cache_need() const override { return CacheNeed::state({heads_, dim_, vdim_}, DType::F32); }
+    // per head [value_dim][padded head_dim]: the kernel's threads own 16 key channels each, a power of two of them per column
+    int64_t padded_dim() const {
+        int64_t parts = 1;
+        while (parts * 16 < dim_) parts *= 2;
+        return parts * 16;
+    }
+    CacheNeed cache_need() const override { return CacheNeed::state({heads_, vdim_, padded_dim()}, DType::F32); }
+
+    // A step with a long prompt portion cuts every request's rows into chunks for the recurrence (first row, rows, segment,
+    // 1 on the request's last chunk) so that a prompt's tokens are spread over the device: the chunk list is this mixer's
+    // own metadata, shared by all layers of its kind.
+    void prepare_step(StepPlan& plan) override {
+        if (plan.has("decayed.chunks")) return;
+        int longest = 0;
+        for (int n : plan.q_lens) longest = std::max(longest, n);
+        if (longest < kChunkFrom) return;
+        std::vector<int32_t> items, seg_items = {0};
+        int row = 0;
+        for (int s = 0; s < plan.S; s++) {
+            const int n = plan.q_lens[s];
+            for (int at = 0; at < n; at += kChunk) {
+                items.push_back(row + at); items.push_back(std::min(kChunk, n - at)); items.push_back(s); items.push_back(at + kChunk >= n);
+            }
+            row += n;
+            seg_items.push_back((int32_t)(items.size() / 4));
+        }
+        plan.add("decayed.chunks", std::move(items));
+        plan.add("decayed.seg_chunks", std::move(seg_items));
+    }
 
     Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
-        const int64_t per_slot = (int64_t)heads_ * dim_ * vdim_;
+        const int64_t per_slot = (int64_t)heads_ * padded_dim() * vdim_;
         if (!cache.state.defined() || cache.state.dtype != DType::F32 || cache.state.numel() != (int64_t)cache.state.shape[0] * per_slot)
             throw Error(kInvalidState, "gated_linear_attention: the cache manager gave no state of this mixer's shape");
         const int T = ctx.T;
@@ -100,17 +128,27 @@ public:
         Tensor y = ws.get("gla_o", {T, value_width_}, dt);
         const size_t es = dtype_size(dt);
         char* base = static_cast<char*>(qkvg.data);
+        const StepArray chunks = ctx.array("decayed.chunks"), seg_chunks = ctx.array("decayed.seg_chunks");
+        const int n_chunks = chunks.count / 4;
+        float *carry = nullptr, *decay = nullptr;
+        if (n_chunks) {
+            carry = ws.get("gla_carry", {n_chunks, heads_, vdim_, padded_dim()}, DType::F32).as<float>();
+            decay = ws.get("gla_chunk_decay", {n_chunks, heads_, dim_}, DType::F32).as<float>();
+        }
         if (LaunchProfile::get().on())      // q, k, v, g and the decay's logits in, o out twice (raw and gated), the state in and out
             LaunchProfile::get().note_cost((double)T * (width * es + key_width_ * 4.0 + value_width_ * (8.0 + es)) + 2.0 * ctx.S * per_slot * 4.0,
                                            (double)T * heads_ * dim_ * vdim_ * 5.0);
         QE_LAUNCH(k, k.decayed_scan(base, base + key_width_ * es, base + 2 * key_width_ * es, base + (2 * key_width_ + value_width_) * es,
                                     qkvg.code(), width, z.as<float>(), key_width_, decay_bias_.as<float>(), (float)tau_,
                                     (float)(1.0 / std::sqrt((double)dim_)), norm_.as<float>(), (float)eps_, cache.state.as<float>(), per_slot,
-                                    ctx.seg_start, ctx.seg_slot, ctx.S, T, heads_, dim_, vdim_, raw.as<float>(), y.data, ctx.stream));
+                                    ctx.seg_start, ctx.seg_slot, ctx.S, T, heads_, dim_, vdim_, n_chunks ? chunks.data : nullptr, n_chunks,
+                                    n_chunks ? seg_chunks.data : nullptr, carry, decay, raw.as<float>(), y.data, ctx.stream));
         return o_proj_(y, ctx, "gla_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 
 private:
+    static constexpr int kChunk = 64;           // tokens of a chunk of the recurrence
+    static constexpr int kChunkFrom = 128;      // the longest portion of a step from which the recurrence runs in chunks
     int64_t hidden_, key_width_, value_width_, rank_;
     int heads_, dim_, vdim_;
     double tau_, eps_;
