@@ -74,7 +74,7 @@ public:
             if (heads % kv)
                 throw ConfigError("config.json: " + where + "mixer.left: " + std::to_string(heads) + " heads are not a multiple of " + std::to_string(kv) + " kv_heads");
             const Json& rot = object_at(left, "rot", where + "mixer.left.");
-            const long long dims = take_int(rot, "dims", 2);
+            const long long dims = take_int(rot, "dims", 0);          // 0: no dimension is rotated
             if (dims % 2 || dims > dim) throw ConfigError("config.json: " + where + "mixer.left.rot.dims must be even and at most dim");
             if (!(take_float(rot, "base") > 0)) throw ConfigError("config.json: " + where + "mixer.left.rot.base must be positive");
             take_int(object_at(left, "mask", where + "mixer.left."), "size");
@@ -161,12 +161,16 @@ public:
             a.set("window", Json());
             a.set("chunk", left.at("mask").at("size"));
             a.set("scale", left.at("scale"));
-            Json pos = Json::object();
-            pos.set("theta", left.at("rot").at("base"));
-            pos.set("n_rot", left.at("rot").at("dims"));
-            pos.set("max_position", max_position);
-            pos.set("pairing", "half");
-            a.set("position", PartSpec("rope_neox", pos).to_json());
+            if (left.at("rot").at("dims").as_int() > 0) {
+                Json pos = Json::object();
+                pos.set("theta", left.at("rot").at("base"));
+                pos.set("n_rot", left.at("rot").at("dims"));
+                pos.set("max_position", max_position);
+                pos.set("pairing", "half");
+                a.set("position", PartSpec("rope_neox", pos).to_json());
+            } else {
+                a.set("position", Json());
+            }
             const std::string lp = p + "mix.left.";
             a.set("names", names({{"q_proj", lp + "q"}, {"k_proj", lp + "k"}, {"v_proj", lp + "v"}, {"o_proj", lp + "o"},
                                   {"q_bias", lp + "q.b"}, {"k_bias", lp + "k.b"}, {"v_bias", lp + "v.b"},

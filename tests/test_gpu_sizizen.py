@@ -543,3 +543,23 @@ def test_the_choice_goes_by_corrected_scores_within_the_best_groups_and_the_weig
         by_hand = sum(s[e] * P.squared_relu_expert(h, f64(ww), f"l0.mlp.e{e}.") for e in chosen) + P.squared_relu_expert(h, f64(ww), "l0.mlp.shared.")
         close(ref, by_hand, 1e-6)
         close(p.feed_forward(x), ref, 1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_left_mixer_that_rotates_nothing_and_layers_in_another_order(tmp_path, dtype):
+    """rot.dims 0 (no position encoding at all), a routed layer first, a layer without a feed-forward in the middle."""
+    cfg = config(64, 50, [
+        (left(4, 1, 16, 16, 0, 7), right(2, 16, 16, 2.0, 8), moe(16, 4, 2, 2, 1, 32)),
+        (left(2, 2, 32, 8, 32, 20), right(1, 32, 64, 5.0, 4), None),
+        (left(8, 4, 8, 8, 4, 3), right(4, 16, 8, 1.0, 16), dense(96)),
+    ])
+    w = draw_weights(cfg, 77)
+    if dtype == "bfloat16":
+        w = steady_choice(cfg, w, 3)
+    folder = make_folder(tmp_path, cfg, w, "F32" if dtype == "float32" else "BF16")
+    eng = engine_for(folder, dtype)
+    toks = tokens(90, cfg["vocab"], 4)
+    ref = P.forward(cfg, f64(w), toks)
+    close(run_cut(eng, "whole", toks, []), ref, TOL[dtype])
+    close(run_cut(eng, "cut", toks, [2, 19, 1, 1, 40, 2]), ref, TOL[dtype])
+    eng.close()
