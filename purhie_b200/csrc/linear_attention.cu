@@ -403,6 +403,8 @@ PH_EXPORT int ph_decayed_scan(const void* q, const void* k, const void* v, const
     const int unit = CPT * 32 / parts;                             // columns of one warp
     int cols = (DV + unit - 1) / unit * unit;
     if (cols / CPT * parts > MAX_THREADS) cols = MAX_THREADS / parts * CPT;
+    // a narrow head with many key channels: idle columns, so that the block has the threads to fetch a token's values
+    while (3 * D + cols > LOADS * (cols / CPT * parts) && (cols + unit) / CPT * parts <= MAX_THREADS) cols += unit;
     const int threads = cols / CPT * parts;
     int tile = 16;
     while (tile > 1 && tile * (3 * D + cols) > LOADS * threads) tile /= 2;

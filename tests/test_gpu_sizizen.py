@@ -563,3 +563,22 @@ def test_a_left_mixer_that_rotates_nothing_and_layers_in_another_order(tmp_path,
     close(run_cut(eng, "whole", toks, []), ref, TOL[dtype])
     close(run_cut(eng, "cut", toks, [2, 19, 1, 1, 40, 2]), ref, TOL[dtype])
     eng.close()
+
+
+@pytest.mark.parametrize("heads,dim,vdim", [(1, 128, 256), (2, 256, 128), (1, 512, 8), (3, 20, 130), (1, 72, 5)])
+def test_states_too_large_for_one_block_and_odd_widths(tmp_path, heads, dim, vdim):
+    """A head whose columns are spread over several blocks (the head norm then runs as a launch of its own), key channels
+    that need 16 or 32 threads a column, value widths that are no multiple of four; whole, cut, and long enough for the
+    chunked passes."""
+    from purhie_b200.parts import PartProbe
+    cfg = config(32, 20, [(left(1, 1, 8, 8, 4, 16), right(heads, dim, vdim, 6.0, 4), None)])
+    w = draw_weights(cfg, heads * 1000 + dim)
+    folder = make_folder(tmp_path, cfg, w)
+    m = cfg["layers"][0]["mixer"]["right"]
+    x = np.random.default_rng(dim).normal(0, 1.0, (150, 32)).astype(np.float32)
+    ref = P.right_mixer(x.astype(np.float64), f64(w), "l0.mix.right.", m, cfg["norm"]["eps"])
+    p = PartProbe("mixer", "gated_linear_attention", part_of(cfg, 0, "mixer")[1]["right"]["params"])
+    p.bind_folder(folder)
+    p.mixer_cache(8, 4, 2)
+    close(mixer_in_pieces(p, x, [150]), ref, 2e-4)                       # chunks of 64, 64 and 22
+    close(mixer_in_pieces(p, x, [1, 2, 17, 129, 1], request=2), ref, 2e-4)
